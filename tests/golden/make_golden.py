@@ -1,0 +1,195 @@
+"""Generate the golden fixtures in this folder by running the reference's own eager PyTorch path on CPU.
+
+Usage (in a container that has the reference project checked out):
+
+    python tests/golden/make_golden.py --reference <path to the reference project root>
+
+The reference ships no golden vectors for its attention path, so parity is pinned to what its code
+computes: this script imports ``LlamaNAtSChunkAttentionLayer`` and ``NAtSCache`` from the reference
+(with four stub modules for files the reference imports but does not ship, and a stubbed device-capability
+query because there is no GPU where this runs), drives them exactly as ``AttentionLayer.forward`` does in
+eval mode (prepare_kv -> repeat_kv_values -> multi_head_attention, i.e. cache.update -> generate_mask ->
+scaled_dot_product_attention -> cache.post_update), and stores inputs' seeds, role codes, outputs and the
+cache state after the prefill and after a run of single-token decode steps.
+
+Inputs are regenerated from the stored seed by ``golden_inputs`` below (imported by the tests); a float64
+checksum of every regenerated tensor is stored next to the outputs so that generator drift is detected.
+"""
+from __future__ import annotations
+
+import argparse
+import os
+import sys
+import types
+
+import numpy as np
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+# name -> (B, Hq, Hkv, N, D, C, SW, p_global, p_local, seed, n_decode, special)
+CASES = {
+    # tiny cases: complete tensors are stored
+    'tiny_mha':       dict(B=2, Hq=2, Hkv=2, N=96,  D=16, C=8,  SW=32, pg=0.10, pl=0.30, seed=1, n_decode=20),
+    'tiny_gqa':       dict(B=2, Hq=4, Hkv=2, N=128, D=16, C=16, SW=32, pg=0.10, pl=0.30, seed=2, n_decode=40),
+    'tiny_ragged':    dict(B=2, Hq=4, Hkv=2, N=200, D=16, C=16, SW=64, pg=0.10, pl=0.30, seed=3, n_decode=30),
+    'tiny_short':     dict(B=1, Hq=2, Hkv=2, N=40,  D=16, C=8,  SW=64, pg=0.20, pl=0.30, seed=4, n_decode=20),
+    'tiny_sub_chunk': dict(B=1, Hq=2, Hkv=2, N=5,   D=16, C=8,  SW=16, pg=0.20, pl=0.30, seed=5, n_decode=30),
+    'all_local':      dict(B=1, Hq=2, Hkv=2, N=64,  D=16, C=8,  SW=16, pg=0.0,  pl=1.0,  seed=6, n_decode=20, special='all_local'),
+    'all_sliding':    dict(B=1, Hq=2, Hkv=2, N=64,  D=16, C=8,  SW=16, pg=0.0,  pl=0.0,  seed=7, n_decode=20, special='all_sliding'),
+    'all_global':     dict(B=1, Hq=2, Hkv=2, N=64,  D=16, C=8,  SW=16, pg=1.0,  pl=0.0,  seed=8, n_decode=20, special='all_global'),
+    'no_global':      dict(B=2, Hq=2, Hkv=2, N=96,  D=16, C=8,  SW=32, pg=0.0,  pl=0.4,  seed=9, n_decode=20, special='no_global'),
+    # kernel-sized cases (head_dim 64 / 128): every 5th output row is stored
+    'k64_mha':        dict(B=1, Hq=4, Hkv=4, N=512, D=64,  C=64,  SW=256, pg=0.10, pl=0.30, seed=11, n_decode=70),
+    'k128_gqa':       dict(B=1, Hq=4, Hkv=1, N=640, D=128, C=128, SW=256, pg=0.10, pl=0.20, seed=12, n_decode=0),
+    'k64_ragged':     dict(B=2, Hq=4, Hkv=2, N=300, D=64,  C=16,  SW=64,  pg=0.10, pl=0.30, seed=13, n_decode=40),
+    'k128_decode':    dict(B=2, Hq=4, Hkv=2, N=256, D=128, C=32,  SW=64,  pg=0.15, pl=0.30, seed=14, n_decode=70),
+}
+ROW_STRIDE = 5
+
+
+def golden_roles(case: dict) -> np.ndarray:
+    sys.path.insert(0, os.path.join(HERE, '..', '..'))
+    from oracle.nats_oracle import make_roles
+    Nc = -(-case['N'] // case['C'])
+    sp = case.get('special')
+    if sp == 'all_local':
+        return np.full((case['B'], case['Hkv'], Nc), 1, np.uint8)
+    if sp == 'all_sliding':
+        return np.full((case['B'], case['Hkv'], Nc), 2, np.uint8)
+    if sp == 'all_global':
+        return np.zeros((case['B'], case['Hkv'], Nc), np.uint8)
+    roles = make_roles(case['B'], case['Hkv'], Nc, max(case['pg'], 1e-3), max(case['pl'], 1e-3), case['seed'],
+                       force_first_global=(sp != 'no_global'))
+    if sp == 'no_global':
+        roles[roles == 0] = 2
+    if case['N'] % case['C']:
+        roles[..., -1] = 0        # the layer marks an unfinished last chunk global (nats_chunk_attention.py:92-94)
+    return roles
+
+
+def golden_inputs(case: dict):
+    """q [B,Hq,N,D], k, v [B,Hkv,N,D] fp32 and, per decode step, (q1,k1,v1,role codes [B,Hkv])."""
+    g = torch.Generator().manual_seed(case['seed'])
+    B, Hq, Hkv, N, D = case['B'], case['Hq'], case['Hkv'], case['N'], case['D']
+    q = torch.randn(B, Hq, N, D, generator=g)
+    k = torch.randn(B, Hkv, N, D, generator=g)
+    v = torch.randn(B, Hkv, N, D, generator=g)
+    steps = []
+    for _ in range(case['n_decode']):
+        q1 = torch.randn(B, Hq, 1, D, generator=g)
+        k1 = torch.randn(B, Hkv, 1, D, generator=g)
+        v1 = torch.randn(B, Hkv, 1, D, generator=g)
+        r1 = torch.randn(B, Hkv, 3, generator=g).argmax(-1).to(torch.uint8).numpy()
+        sp = case.get('special')
+        if sp == 'all_sliding':
+            r1[:] = 2
+        steps.append((q1, k1, v1, r1))
+    return q, k, v, steps
+
+
+def checksum(*tensors) -> np.ndarray:
+    return np.array([float(t.double().sum()) for t in tensors])
+
+
+def load_reference(root: str):
+    def stub(name, **attrs):
+        m = types.ModuleType(name)
+        m.__path__ = []
+        for key, val in attrs.items():
+            setattr(m, key, val)
+        sys.modules[name] = m
+    stub('nats.components.cache.triton')
+    stub('nats.components.cache.triton.update_one_step', post_update_one_step=None)
+    stub('nats.models.transformer.triton.flashattention_mask_on_chip', nats_attention=None)
+    stub('nats.models.transformer.triton.nats_chunk_attention', nats_chunk_attention=None)
+    torch.cuda.get_device_capability = lambda *a, **k: (10, 0)
+    torch.cuda.empty_cache = lambda *a, **k: None
+    sys.path.insert(0, os.path.join(root, 'src'))
+    from nats.components.cache.dyn_cache import NAtSCache
+    from nats.models.transformer.attention.nats_chunk_attention import LlamaNAtSChunkAttentionLayer
+    return NAtSCache, LlamaNAtSChunkAttentionLayer
+
+
+def state_of(layer_cache) -> dict:
+    n_ctx = int(layer_cache.n_ctx_data)
+    return dict(
+        cache_k=layer_cache.cache_k.detach().numpy().copy(),
+        cache_v=layer_cache.cache_v.detach().numpy().copy(),
+        valid=layer_cache.valid_tokens.numpy().copy(),
+        size_global=layer_cache.size_global_kv.numpy().copy(),
+        size_local=layer_cache.size_local_kv.numpy().copy(),
+        n_ctx_data=np.int64(n_ctx),
+        chunk_fill=np.int64(layer_cache.chunk_fill_size),
+        tail=np.int64(layer_cache.sliding_queue_tail),
+        seen=np.int64(layer_cache._seen_tokens),
+    )
+
+
+def run_case(name: str, case: dict, NAtSCache, Layer) -> dict:
+    from oracle.nats_oracle import onehot_from_roles
+    B, Hq, Hkv, N, D, C, SW = (case[x] for x in ('B', 'Hq', 'Hkv', 'N', 'D', 'C', 'SW'))
+    roles = golden_roles(case)
+    q, k, v, steps = golden_inputs(case)
+    layer = Layer(dim=Hq * D, n_heads=Hq, n_kv_heads=Hkv, layer_id=0, local_seq_max_length=SW, chunk_size=C)
+    layer.eval()
+    cache = NAtSCache(sliding_window_size=SW, chunk_size=C)
+    out = {'roles': roles, 'in_checksum': checksum(q, k, v)}
+    with torch.no_grad():
+        info = {'token_states_info': onehot_from_roles(roles)}
+        keys, values = layer.prepare_kv(q, k, v, 0, cache=cache, kwargs=info)
+        mask = cache.generate_mask(0, N).numpy().copy()          # the reference's ground-truth mask
+        keys, values = layer.repeat_kv_values(keys, values)
+        o = layer.multi_head_attention(q, keys, values, cache=cache, kwargs=info)
+        lc = cache.cache_model[0]
+        tiny = D < 64
+        out['prefill_out'] = o.numpy() if tiny else o[:, :, ::ROW_STRIDE].numpy()
+        if tiny:
+            out['prefill_mask'] = np.packbits(mask, axis=-1)
+        else:
+            out['prefill_mask_rows'] = np.packbits(mask[:, :, ::ROW_STRIDE], axis=-1)
+        for key, val in state_of(lc).items():
+            if tiny or key not in ('cache_k', 'cache_v'):       # kernel-sized cases keep the index-level state only
+                out['pre_' + key] = val
+        dec_out, dec_nctx, dec_sizes = [], [], []
+        fill = int(lc.chunk_fill_size)
+        for (q1, k1, v1, r1) in steps:
+            fill += 1
+            done = fill == C
+            role_now = r1 if done else np.zeros_like(r1)          # placeholder one-hot(global), :81-84
+            if done:
+                fill = 0
+            info1 = {'token_states_info': onehot_from_roles(role_now[..., None])}
+            keys, values = layer.prepare_kv(q1, k1, v1, 0, cache=cache, kwargs=info1)
+            keys, values = layer.repeat_kv_values(keys, values)
+            o1 = layer.multi_head_attention(q1, keys, values, cache=cache, kwargs=info1)
+            dec_out.append(o1.numpy().copy())
+            dec_nctx.append(int(lc.n_ctx_data))
+            dec_sizes.append(np.stack([lc.size_global_kv.numpy().copy(), lc.size_local_kv.numpy().copy()]))
+        if steps:
+            out['dec_out'] = np.stack(dec_out)
+            out['dec_nctx'] = np.array(dec_nctx)
+            out['dec_sizes'] = np.stack(dec_sizes)
+            out['dec_roles'] = np.stack([s[3] for s in steps])
+            out['dec_checksum'] = np.array([checksum(*s[:3]) for s in steps])
+            for key, val in state_of(lc).items():
+                if tiny or key not in ('cache_k', 'cache_v'):
+                    out['post_' + key] = val
+    return out
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument('--reference', required=True)
+    args = ap.parse_args()
+    sys.path.insert(0, os.path.join(HERE, '..', '..'))
+    NAtSCache, Layer = load_reference(args.reference)
+    for name, case in CASES.items():
+        res = run_case(name, case, NAtSCache, Layer)
+        path = os.path.join(HERE, name + '.npz')
+        np.savez_compressed(path, **res)
+        print(f'{name}: {os.path.getsize(path) / 1024:.1f} KiB')
+
+
+if __name__ == '__main__':
+    main()

@@ -1,0 +1,22 @@
+"""Helpers shared by the tests that read the committed golden fixtures."""
+import os
+import sys
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.join(HERE, 'golden'))
+import make_golden  # noqa: E402  (the generator also defines how inputs are regenerated from a seed)
+
+CASES = make_golden.CASES
+ROW_STRIDE = make_golden.ROW_STRIDE
+
+
+def load(name):
+    """(case dict, fixture dict, (q, k, v, steps)) with the regenerated inputs checked against the stored checksums."""
+    case = CASES[name]
+    fx = dict(np.load(os.path.join(HERE, 'golden', name + '.npz')))
+    q, k, v, steps = make_golden.golden_inputs(case)
+    np.testing.assert_allclose(make_golden.checksum(q, k, v), fx['in_checksum'], rtol=0, atol=1e-6,
+                               err_msg='seeded inputs no longer match the ones the fixture was made from')
+    return case, fx, (q, k, v, steps)

@@ -1,0 +1,119 @@
+"""Pins the CPU oracle against the committed outputs of the reference's own eager path (tests/golden)."""
+import numpy as np
+import pytest
+import torch
+
+from golden_util import CASES, ROW_STRIDE, load
+from oracle import nats_oracle as orc
+
+TINY = [n for n, c in CASES.items() if c['D'] < 64]
+KERNEL = [n for n, c in CASES.items() if c['D'] >= 64]
+
+
+def _run_oracle_prefill(case, roles, q, k, v):
+    st = orc.ChunkCacheOracle(case['B'], case['Hkv'], case['SW'], case['C'])
+    st.update(k.numpy(), v.numpy(), roles)
+    out = orc.prefill_attention(q, k, v, roles, case['C'], case['SW'])
+    st.post_update(case['N'])
+    return st, out
+
+
+def _check_state(st, fx, prefix, full):
+    assert np.array_equal(st.size_global, fx[prefix + 'size_global'])
+    assert np.array_equal(st.size_local, fx[prefix + 'size_local'])
+    assert st.n_ctx_data == int(fx[prefix + 'n_ctx_data'])
+    assert st.chunk_fill == int(fx[prefix + 'chunk_fill'])
+    assert st.tail == int(fx[prefix + 'tail'])
+    assert st.seen == int(fx[prefix + 'seen'])
+    assert np.array_equal(st.valid, fx[prefix + 'valid'])
+    if full:        # the whole physical cache, stale regions included: the restatement moves data as the reference does
+        assert np.array_equal(st.cache_k, fx[prefix + 'cache_k'])
+        assert np.array_equal(st.cache_v, fx[prefix + 'cache_v'])
+
+
+@pytest.mark.parametrize('name', TINY + KERNEL)
+def test_prefill_mask_matches_reference(name):
+    case, fx, _ = load(name)
+    m = orc.visible_mask(fx['roles'], case['C'], case['SW'], case['N'])
+    if 'prefill_mask' in fx:
+        ref = np.unpackbits(fx['prefill_mask'], axis=-1)[..., :case['N']].astype(bool)
+    else:
+        ref = np.unpackbits(fx['prefill_mask_rows'], axis=-1)[..., :case['N']].astype(bool)
+        m = m[:, :, ::ROW_STRIDE]
+    assert np.array_equal(m, ref)
+
+
+@pytest.mark.parametrize('name', TINY + KERNEL)
+def test_prefill_output_and_eviction_match_reference(name):
+    case, fx, (q, k, v, _) = load(name)
+    st, out = _run_oracle_prefill(case, fx['roles'], q, k, v)
+    ref = fx['prefill_out']
+    got = out.numpy() if case['D'] < 64 else out[:, :, ::ROW_STRIDE].numpy()
+    np.testing.assert_allclose(got, ref, rtol=1e-4, atol=2e-5)
+    _check_state(st, fx, 'pre_', full=case['D'] < 64)
+
+
+@pytest.mark.parametrize('name', [n for n in TINY + KERNEL if CASES[n]['n_decode'] > 0])
+def test_decode_steps_match_reference(name):
+    case, fx, (q, k, v, steps) = load(name)
+    st, _ = _run_oracle_prefill(case, fx['roles'], q, k, v)
+    C = case['C']
+    for i, (q1, k1, v1, r1) in enumerate(steps):
+        done = st.chunk_fill + 1 == C
+        role_now = (r1 if done else np.zeros_like(r1))[..., None]
+        st.update(k1.numpy(), v1.numpy(), role_now)
+        o = orc.decode_attention(q1, st.cache_k, st.cache_v, st.decode_mask())
+        st.post_update(1)
+        np.testing.assert_allclose(o.numpy(), fx['dec_out'][i], rtol=1e-4, atol=2e-5, err_msg=f'step {i}')
+        assert st.n_ctx_data == int(fx['dec_nctx'][i]), f'step {i}'
+        assert np.array_equal(np.stack([st.size_global, st.size_local]), fx['dec_sizes'][i]), f'step {i}'
+    # final state; the physical cache is compared over the region the reference defines
+    _check_state(st, fx, 'post_', full=False)
+    if case['D'] < 64:
+        n = st.n_ctx_data
+        lens = st.lens()
+        t0 = n // C * C
+        for b in range(case['B']):
+            for h in range(case['Hkv']):
+                for sl in (slice(0, lens[b, h]), slice(t0, n)):
+                    assert np.array_equal(st.cache_k[b, h, sl], fx['post_cache_k'][b, h, sl])
+                    assert np.array_equal(st.cache_v[b, h, sl], fx['post_cache_v'][b, h, sl])
+
+
+def test_kept_tiles_match_dense_mask():
+    roles = orc.make_roles(2, 2, 16, 0.1, 0.3, seed=3)
+    C, SW, N = 64, 256, 1024
+    m = orc.visible_mask(roles, C, SW, N)
+    t = m.reshape(2, 2, 8, 128, 8, 128).any((3, 5)).sum((-1, -2))
+    assert np.array_equal(t, orc.kept_tiles(roles, C, SW, N, 128))
+
+
+def test_decode_equals_one_shot_prefill():
+    """prefill + eviction + decode over the compacted cache == dense attention under the prefill mask."""
+    B, Hq, Hkv, D, C, SW, N0, steps = 2, 4, 2, 16, 8, 32, 64, 48
+    g = torch.Generator().manual_seed(0)
+    N = N0 + steps
+    q = torch.randn(B, Hq, N, D, generator=g, dtype=torch.float64)
+    k = torch.randn(B, Hkv, N, D, generator=g, dtype=torch.float64)
+    v = torch.randn(B, Hkv, N, D, generator=g, dtype=torch.float64)
+    roles = orc.make_roles(B, Hkv, N // C, 0.15, 0.3, seed=5)
+    m = torch.from_numpy(orc.visible_mask(roles, C, SW, N))
+    sc = torch.einsum('bgrsd,bgld->bgrsl', q.view(B, Hkv, 2, N, D), k) / D ** 0.5
+    sc = sc.masked_fill(~m[:, :, None], float('-inf'))
+    full = torch.einsum('bgrsl,bgld->bgrsd', torch.softmax(sc, -1), v).reshape(B, Hq, N, D)
+    st = orc.ChunkCacheOracle(B, Hkv, SW, C)
+    st.update(k[:, :, :N0].numpy(), v[:, :, :N0].numpy(), roles[..., :N0 // C])
+    st.post_update(N0)
+    for i in range(steps):
+        t = N0 + i
+        done = st.chunk_fill + 1 == C
+        role_now = roles[..., t // C][..., None] if done else np.zeros((B, Hkv, 1), np.uint8)
+        st.update(k[:, :, t:t + 1].numpy(), v[:, :, t:t + 1].numpy(), role_now)
+        mask = st.decode_mask()
+        kk = torch.from_numpy(st.cache_k[:, :, :mask.shape[-1]].copy())
+        vv = torch.from_numpy(st.cache_v[:, :, :mask.shape[-1]].copy())
+        s1 = torch.einsum('bgrd,bgld->bgrl', q[:, :, t].view(B, Hkv, 2, D), kk) / D ** 0.5
+        s1 = s1.masked_fill(~torch.from_numpy(mask)[:, :, None], float('-inf'))
+        o = torch.einsum('bgrl,bgld->bgrd', torch.softmax(s1, -1), vv).reshape(B, Hq, D)
+        st.post_update(1)
+        assert (o - full[:, :, t]).abs().max() < 1e-12, i
