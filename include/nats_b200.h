@@ -1,0 +1,150 @@
+/* C-ABI of libnats_b200: the NAtS attention hot path (role-masked chunked prefill, KV-cache
+ * eviction, decode over the compacted ragged cache) as hand-written CUDA for sm_100a.
+ *
+ * Conventions
+ *   - every pointer named d_* is DEVICE memory owned by the caller; nothing here allocates or frees
+ *     device memory (one exception is documented at the entry point that carries static scratch);
+ *   - tensors are dense row-major with the shapes given, bf16 unless stated otherwise;
+ *   - role codes are uint8: 0 = global, 1 = local, 2 = sliding window (the column order of the
+ *     reference's one-hot ``token_states_info``, src/nats/components/cache/nats_chunk_layer_cache.py:188-190);
+ *   - ``stream`` is a cudaStream_t passed as void*; work is only enqueued, never synchronised;
+ *   - the return value is 0 on success, else one of NATS_ERR_*; nats_b200_last_error() gives the text;
+ *   - kernels that wait on hardware barriers bound every wait and report a time-out through the
+ *     caller's device status word (0 = ok) instead of spinning forever.
+ *
+ * File paths in the comments below are relative to the reference project root.
+ */
+#ifndef NATS_B200_H_
+#define NATS_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define NATS_OK               0
+#define NATS_ERR_INVALID_ARG  1   /* shape / alignment / null pointer */
+#define NATS_ERR_UNSUPPORTED  2   /* valid for the reference, not built here (e.g. head_dim 256) */
+#define NATS_ERR_CUDA         3   /* a CUDA runtime / driver call failed */
+#define NATS_ERR_WORKSPACE    4   /* workspace too small */
+
+#define NATS_ROLE_GLOBAL  0
+#define NATS_ROLE_LOCAL   1
+#define NATS_ROLE_SLIDING 2
+
+/* Thread-local text of the last error returned on this host thread ("" if none). */
+const char* nats_b200_last_error(void);
+
+/* Compile-time facts: "sm_100a", tile sizes, limits.  Never fails. */
+const char* nats_b200_build_info(void);
+
+/* ------------------------------------------------------------------------------------------------
+ * Role mask metadata.
+ * Replaces: generate_hard_seq_masks (src/nats/components/masks/utils.py:81-94) and the sliding-window
+ * part of NAtSChunkLayerCache._generate_local_mask (src/nats/components/cache/nats_chunk_layer_cache.py:589-620)
+ * -- instead of a dense [N,N] bool mask it produces, per KV chunk c, the last query row that may still
+ * see the chunk (INT32_MAX for global chunks and for the last chunk), and per 128-column KV tile the
+ * max / min of those limits, which is all the prefill kernel needs to skip or to mask a tile.
+ *   d_roles      uint8 [B,Hkv,Nc], Nc = ceil(N/C)
+ *   d_lim        int32 [B,Hkv,Nc]            (out)
+ *   d_tile_max   int32 [B,Hkv,Nt], Nt = ceil(N/128)   (out)
+ *   d_tile_min   int32 [B,Hkv,Nt]            (out)
+ *   d_kept_tiles int64 [B,Hkv] or NULL       (out) number of 128x128 (q tile, kv tile) pairs the prefill computes
+ */
+int nats_b200_role_prep(const uint8_t* d_roles, int B, int Hkv, int N, int C, int SW,
+                        int32_t* d_lim, int32_t* d_tile_max, int32_t* d_tile_min, int64_t* d_kept_tiles,
+                        void* stream);
+
+/* Bytes of workspace nats_b200_prefill_fwd needs (lim + tile_max + tile_min, 256-byte aligned parts). */
+size_t nats_b200_prefill_workspace_bytes(int B, int Hkv, int N, int C);
+
+/* Role-masked causal flash attention of the first prefill call.
+ * Replaces: nats_prefill without past (src/nats/models/transformer/triton/nats_flashattn_fwd.py:617-692),
+ * nats_chunk_attention forward (src/nats/models/transformer/triton/nats_chunk_attention.py:1154-1185) and the
+ * eager pair generate_mask + scaled_dot_product_attention
+ * (src/nats/models/transformer/attention/nats_chunk_attention.py:130-142).  The mask is the eager one.
+ *   d_q [B,Hq,N,D], d_k,d_v [B,Hkv,N,D], d_o [B,Hq,N,D]  bf16, 16-byte aligned; D in {64,128}; Hq % Hkv == 0
+ *   d_roles uint8 [B,Hkv,ceil(N/C)];  SW % C == 0;  N <= 524288
+ *   d_workspace: nats_b200_prefill_workspace_bytes bytes;  d_kept_tiles int64 [B,Hkv] or NULL
+ *   d_status: one int32, must be 0 on entry; non-zero afterwards means a bounded wait gave up and d_o is invalid
+ */
+int nats_b200_prefill_fwd(const void* d_q, const void* d_k, const void* d_v, void* d_o, const uint8_t* d_roles,
+                          int B, int Hq, int Hkv, int N, int D, int C, int SW, float sm_scale,
+                          void* d_workspace, size_t workspace_bytes, int64_t* d_kept_tiles, int32_t* d_status,
+                          void* stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * Eviction after the first prefill call, in two steps because the size of the compacted cache is data dependent.
+ *
+ * Step 1 -- keep-set and ranks.  Replaces NAtSChunkLayerCache.get_updated_cache_info
+ * (src/nats/components/cache/nats_chunk_layer_cache.py:715-868) and the size bookkeeping of _post_update (:352-358).
+ * Kept chunks of a (b,kv-head), in order: every global chunk, then the local chunks after the last global one;
+ * an unfinished last chunk (N % C != 0) is never kept.
+ *   d_rank         int32 [B,Hkv,Nc]  (out) destination chunk slot counted from the end of the ring, or -1
+ *   d_size_global  int64 [B,Hkv]     (out) SW + C * #global
+ *   d_size_local   int64 [B,Hkv]     (out) C * #(local after the last global)
+ *   d_state        int32 [4]         (in/out) cache state words, all zero before the first call:
+ *                                    [0] = max over (b,h) of size_global + size_local (the common tail offset T0),
+ *                                    [1],[2] = scratch of the cross-block reduction (zero between calls), [3] reserved
+ */
+int nats_b200_evict_plan(const uint8_t* d_roles, int B, int Hkv, int N, int C, int SW,
+                         int32_t* d_rank, int64_t* d_size_global, int64_t* d_size_local, int32_t* d_state,
+                         void* stream);
+
+/* Step 2 -- data movement.  Replaces the first-call cache build of NAtSChunkLayerCache.update (:215-237),
+ * move_sliding_window_tokens_to_head (:391-437), merge_local_to_global_caches
+ * (src/nats/components/cache/cache_update.py:25-76), the tail zeroing (:361-362) and mask_invalid_tokens (:634-656).
+ * Writes, per (b,h):  cache[0,SW) = ring (last SW/C complete chunks; zeros + invalid where the chunk is not a
+ * sliding one), cache[SW,len) = kept chunks, cache[T0,T0+r) = the r = N % C tokens of the unfinished chunk with
+ * T0 = d_state[0], everything else up to Lcap zero;  valid[] accordingly.
+ *   d_k,d_v [B,Hkv,N,D] (source, untouched);  d_cache_k,d_cache_v [B,Hkv,Lcap,D];  d_valid uint8 [B,Hkv,Lcap]
+ *   Lcap >= ceil((T0 + r)/C)*C  (the caller reads d_state[0] back, or passes the bound SW + ceil(N/C)*C)
+ */
+int nats_b200_evict_compact(const void* d_k, const void* d_v, const uint8_t* d_roles, const int32_t* d_rank,
+                            const int64_t* d_size_global, const int64_t* d_size_local, const int32_t* d_state,
+                            int B, int Hkv, int N, int D, int C, int SW,
+                            void* d_cache_k, void* d_cache_v, uint8_t* d_valid, int Lcap, void* stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * Decode over the compacted ragged cache.
+ *
+ * Logical sequence a query of (b,h) attends to (the reference's ``valid_tokens[:, :, :n_ctx_data+1]``,
+ * src/nats/components/cache/nats_chunk_layer_cache.py:622-632): the valid ring slots [0,SW), the kept tokens
+ * [SW,len), the ``fill`` tokens of the unfinished chunk at [T0,T0+fill) and the new token itself.
+ */
+size_t nats_b200_decode_workspace_bytes(int B, int Hq, int Hkv, int D, int max_len);
+
+/* One decode step: append + attention.  Replaces NAtSChunkLayerCache.update for x_len == 1 (:239-256),
+ * _generate_mask_one_step (:622-632) and repeat_kv + scaled_dot_product_attention over the padded cache
+ * (src/nats/models/transformer/attention/nats_chunk_attention.py:131-142).
+ *   d_q [B,Hq,1,D]; d_k_new,d_v_new [B,Hkv,1,D] (written to cache position T0+fill, valid set); d_o [B,Hq,1,D]
+ *   d_state[0] = T0;  fill = tokens already in the unfinished chunk (host knows it);  T0+fill < Lcap
+ *   max_len_bound: host upper bound of T0 (sizes the grid; no host sync needed)
+ *   d_workspace: nats_b200_decode_workspace_bytes(B,Hq,Hkv,D,max_len_bound+C) bytes; must be zero on first use
+ *   (the kernel leaves its counters zero again);  D in {64,128};  Hq/Hkv in {1,2,4,8}
+ */
+int nats_b200_decode_fwd(const void* d_q, const void* d_k_new, const void* d_v_new, void* d_o,
+                         void* d_cache_k, void* d_cache_v, uint8_t* d_valid, int Lcap,
+                         const int64_t* d_size_global, const int64_t* d_size_local, const int32_t* d_state,
+                         int fill, int max_len_bound,
+                         int B, int Hq, int Hkv, int D, int C, int SW, float sm_scale,
+                         void* d_workspace, size_t workspace_bytes, void* stream);
+
+/* Placement of a chunk that has just been completed by a decode step.  Replaces the x_len == 1 branch of
+ * NAtSChunkLayerCache._post_update (:270-330, 356-371) incl. the ring write of move_sliding_window_tokens_to_head.
+ *   d_roles uint8 [B,Hkv]: role of the completed chunk;  tail: ring write position before this call (host tracks it)
+ *   global -> chunk to size_global, size_global += C, size_local = 0;  local -> chunk to size_global+size_local,
+ *   size_local += C;  sliding -> ring only.  d_state[0] becomes the new maximum length (it can shrink: a global
+ *   chunk drops the locals before it).  The reference's joint "every head is sliding" early exit (:283-288)
+ *   changes nothing but the ring, which is what the per-head rule already does.
+ */
+int nats_b200_decode_place(const uint8_t* d_roles, void* d_cache_k, void* d_cache_v, uint8_t* d_valid, int Lcap,
+                           int64_t* d_size_global, int64_t* d_size_local, int32_t* d_state,
+                           int tail, int B, int Hkv, int D, int C, int SW, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif  /* NATS_B200_H_ */

@@ -1,0 +1,411 @@
+// Role-mask metadata, eviction (keep-set ranks + stream compaction) and decode-step chunk placement.
+// All of it is integer / byte work bounded by HBM traffic and launch latency: one block per (batch, kv-head)
+// for the scans, 16-byte vectorised row copies for the data movement.
+#include <stdarg.h>
+
+#include "common.cuh"
+
+namespace nats {
+
+// ---- host-side error text ---------------------------------------------------------------------
+static thread_local char g_err[512] = "";
+char* last_error_buf() { return g_err; }
+int fail(int code, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+constexpr int kScanThreads = 256;
+
+// =================================================================================================
+// role_prep: per-chunk row limit, per-tile max/min limit, kept-tile count
+// =================================================================================================
+__global__ void __launch_bounds__(kScanThreads)
+role_prep_kernel(const uint8_t* __restrict__ roles, int Nc, int N, int C, int SW, int Nt,
+                 int32_t* __restrict__ lim, int32_t* __restrict__ tmax, int32_t* __restrict__ tmin,
+                 long long* __restrict__ kept) {
+    const int bh = blockIdx.x, tid = threadIdx.x;
+    roles += (size_t)bh * Nc;
+    lim += (size_t)bh * Nc;
+    tmax += (size_t)bh * Nt;
+    tmin += (size_t)bh * Nt;
+    __shared__ int s[kScanThreads];
+    __shared__ int carry;
+    __shared__ unsigned long long kept_sm;
+    if (tid == 0) { carry = Nc - 1; kept_sm = 0; }   // the last chunk counts as global for the next-global index
+    __syncthreads();
+    // next-global index by a reversed inclusive min-scan, 256 chunks at a time from the end of the sequence
+    for (int hi = Nc; hi > 0; hi -= kScanThreads) {
+        const int c = hi - 1 - tid;
+        const int role = (c >= 0) ? roles[c] : NATS_ROLE_LOCAL;
+        const bool gf = c >= 0 && (role == NATS_ROLE_GLOBAL || c == Nc - 1);
+        s[tid] = gf ? c : kNoLimit;
+        __syncthreads();
+        for (int o = 1; o < kScanThreads; o <<= 1) {
+            const int v = (tid >= o) ? s[tid - o] : kNoLimit;
+            __syncthreads();
+            s[tid] = min(s[tid], v);
+            __syncthreads();
+        }
+        const int fill = min(s[tid], carry);
+        if (c >= 0) {
+            int l;
+            if (role == NATS_ROLE_SLIDING) {
+                l = (int)min((long long)c * C + SW + C - 1, (long long)kNoLimit);
+            } else if (gf) {
+                l = kNoLimit;
+            } else {
+                l = (int)min(((long long)fill + 1) * C - 1, (long long)kNoLimit);
+            }
+            lim[c] = l;
+        }
+        __syncthreads();
+        if (tid == kScanThreads - 1) carry = fill;
+        __syncthreads();
+    }
+    // per 128-column tile: max / min of the limits of the chunks it overlaps, and how many q tiles keep it
+    unsigned long long mine = 0;
+    for (int kt = tid; kt < Nt; kt += kScanThreads) {
+        const int c0 = (int)(((long long)kt * kTile) / C);
+        const int c1 = (int)(min((long long)kt * kTile + kTile - 1, (long long)N - 1) / C);
+        int mx = -1, mn = kNoLimit;
+        for (int c = c0; c <= c1; ++c) {
+            const int l = lim[c];
+            mx = max(mx, l);
+            mn = min(mn, l);
+        }
+        tmax[kt] = mx;
+        tmin[kt] = mn;
+        const int last_t = min(Nt - 1, mx / kTile);
+        if (last_t >= kt) mine += (unsigned long long)(last_t - kt + 1);
+    }
+    if (kept != nullptr) {
+        atomicAdd(&kept_sm, mine);
+        __syncthreads();
+        if (tid == 0) kept[bh] = (long long)kept_sm;
+    }
+}
+
+// =================================================================================================
+// evict_plan: keep flags -> destination ranks (ballot + prefix sum), sizes, max length
+// =================================================================================================
+__device__ __forceinline__ void publish_max_len(int32_t* state, int len, int nblocks) {
+    // state[1] accumulates the maximum over blocks; the last block to arrive publishes it in state[0]
+    // and leaves the scratch words zero for the next call.  No block ever waits for another.
+    __shared__ int last;
+    if (threadIdx.x == 0) {
+        atomicMax(&state[1], len);
+        __threadfence();
+        const int ticket = atomicAdd(&state[2], 1);
+        last = (ticket == nblocks - 1);
+        if (last) {
+            __threadfence();
+            const int m = atomicExch(&state[1], 0);
+            state[0] = m;
+            state[2] = 0;
+        }
+    }
+}
+
+__global__ void __launch_bounds__(kScanThreads)
+evict_plan_kernel(const uint8_t* __restrict__ roles, int Nc, int n_full, int C, int SW,
+                  int32_t* __restrict__ rank, long long* __restrict__ size_global,
+                  long long* __restrict__ size_local, int32_t* __restrict__ state) {
+    const int bh = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    roles += (size_t)bh * Nc;
+    rank += (size_t)bh * Nc;
+    __shared__ int s_last_g;
+    __shared__ int s_warp[kScanThreads / 32];
+    __shared__ int s_base, s_ng;
+    if (tid == 0) { s_last_g = -1; s_base = 0; s_ng = 0; }
+    __syncthreads();
+    // pass 1: last global chunk among the complete chunks
+    int lg = -1;
+    for (int c = tid; c < n_full; c += kScanThreads)
+        if (roles[c] == NATS_ROLE_GLOBAL) lg = c;
+    for (int o = 16; o > 0; o >>= 1) lg = max(lg, __shfl_xor_sync(0xffffffffu, lg, o));
+    if (lane == 0 && lg >= 0) atomicMax(&s_last_g, lg);
+    __syncthreads();
+    const int last_g = s_last_g;
+    // pass 2: ordered ranks of the kept chunks
+    for (int c0 = 0; c0 < Nc; c0 += kScanThreads) {
+        const int c = c0 + tid;
+        const int role = (c < n_full) ? roles[c] : -1;
+        const bool is_g = role == NATS_ROLE_GLOBAL;
+        const bool keep = is_g || (role == NATS_ROLE_LOCAL && c > last_g);
+        const unsigned m = __ballot_sync(0xffffffffu, keep);
+        const unsigned mg = __ballot_sync(0xffffffffu, is_g);
+        if (lane == 0) s_warp[warp] = __popc(m);
+        if (lane == 0 && mg) atomicAdd(&s_ng, __popc(mg));
+        __syncthreads();
+        int before = s_base;
+        for (int w = 0; w < warp; ++w) before += s_warp[w];
+        if (c < Nc) rank[c] = keep ? before + __popc(m & ((1u << lane) - 1u)) : -1;
+        __syncthreads();
+        if (tid == 0) {
+            int tot = 0;
+            for (int w = 0; w < kScanThreads / 32; ++w) tot += s_warp[w];
+            s_base += tot;
+        }
+        __syncthreads();
+    }
+    const int n_kept = s_base, n_g = s_ng;
+    const long long sg = (long long)SW + (long long)C * n_g;
+    const long long sl = (long long)C * (n_kept - n_g);
+    if (tid == 0) {
+        size_global[bh] = sg;
+        size_local[bh] = sl;
+    }
+    publish_max_len(state, (int)(sg + sl), gridDim.x);
+}
+
+// =================================================================================================
+// evict_compact: ring fill + kept-chunk copies + pending tail + zero / valid bookkeeping
+// =================================================================================================
+constexpr int kCopyThreads = 256;
+constexpr int kTokPerBlock = 64;
+
+struct CompactParams {
+    const uint8_t* k; const uint8_t* v;          // [BH, N, rowB] bytes
+    const uint8_t* roles; const int32_t* rank;   // [BH, Nc]
+    const long long* size_global; const long long* size_local; const int32_t* state;
+    uint8_t* ck; uint8_t* cv; uint8_t* valid;    // [BH, Lcap, rowB], [BH, Lcap]
+    int N, Nc, n_full, C, SW, Lcap, rowB;        // rowB = D * 2 bytes
+    int nA, nB;                                  // blocks in sections A (source tokens) and B (ring)
+};
+
+__global__ void __launch_bounds__(kCopyThreads) evict_compact_kernel(const CompactParams p) {
+    const int bh = blockIdx.y, tid = threadIdx.x;
+    const int vpt = p.rowB >> 4;                          // 16-byte vectors per token row
+    const int tpp = kCopyThreads / vpt;                   // tokens per pass
+    const int trow = tid / vpt, tvec = (tid % vpt) << 4;
+    const uint8_t* k = p.k + (size_t)bh * p.N * p.rowB;
+    const uint8_t* v = p.v + (size_t)bh * p.N * p.rowB;
+    uint8_t* ck = p.ck + (size_t)bh * p.Lcap * p.rowB;
+    uint8_t* cv = p.cv + (size_t)bh * p.Lcap * p.rowB;
+    uint8_t* valid = p.valid + (size_t)bh * p.Lcap;
+    const uint8_t* roles = p.roles + (size_t)bh * p.Nc;
+    const int32_t* rank = p.rank + (size_t)bh * p.Nc;
+    const int base = p.SW / p.C;                          // first chunk slot behind the ring
+    const uint4 zero = make_uint4(0, 0, 0, 0);
+    int blk = blockIdx.x;
+    if (trow >= tpp) return;                              // head dims whose vector count does not divide 256
+    if (blk < p.nA) {
+        // section A: source-driven copy of kept chunks
+        const int t0 = blk * kTokPerBlock;
+        for (int i = trow; i < kTokPerBlock; i += tpp) {
+            const int t = t0 + i;
+            if (t >= p.n_full * p.C) break;
+            const int c = t / p.C;
+            const int r = rank[c];
+            if (r < 0) continue;
+            const size_t dst = ((size_t)(base + r) * p.C + (t - c * p.C)) * p.rowB + tvec;
+            const size_t src = (size_t)t * p.rowB + tvec;
+            st16(ck + dst, ld16_stream(k + src));
+            st16(cv + dst, ld16_stream(v + src));
+        }
+        return;
+    }
+    blk -= p.nA;
+    if (blk < p.nB) {
+        // section B: the ring holds the last min(n_full, SW/C) complete chunks
+        const int n_upd = min(p.n_full, p.SW / p.C);
+        const int n_fills = n_upd * p.C;
+        const int src0 = (p.n_full - n_upd) * p.C;
+        const int s0 = blk * kTokPerBlock;
+        for (int i = trow; i < kTokPerBlock; i += tpp) {
+            const int slot = s0 + i;
+            if (slot >= p.SW) break;
+            bool sw = false;
+            if (slot < n_fills) sw = roles[(src0 + slot) / p.C] == NATS_ROLE_SLIDING;
+            const size_t dst = (size_t)slot * p.rowB + tvec;
+            const size_t src = (size_t)(src0 + slot) * p.rowB + tvec;
+            st16(ck + dst, sw ? ld16_stream(k + src) : zero);
+            st16(cv + dst, sw ? ld16_stream(v + src) : zero);
+            if (tvec == 0) valid[slot] = sw ? 1 : 0;
+        }
+        return;
+    }
+    blk -= p.nB;
+    // section C: destination-driven: [len, Lcap) is zero except the tokens of the unfinished chunk at [T0, T0+rem)
+    const int len = (int)(p.size_global[bh] + p.size_local[bh]);
+    const int T0 = p.state[0];
+    const int rem = p.N - p.n_full * p.C;
+    const int d0 = p.SW + blk * kTokPerBlock;
+    for (int i = trow; i < kTokPerBlock; i += tpp) {
+        const int d = d0 + i;
+        if (d >= p.Lcap) break;
+        const bool in_tail = d >= T0 && d < T0 + rem;
+        if (tvec == 0) valid[d] = (d < len || in_tail) ? 1 : 0;
+        if (d < len) continue;
+        const size_t dst = (size_t)d * p.rowB + tvec;
+        if (in_tail) {
+            const size_t src = (size_t)(p.n_full * p.C + (d - T0)) * p.rowB + tvec;
+            st16(ck + dst, ld16_stream(k + src));
+            st16(cv + dst, ld16_stream(v + src));
+        } else {
+            st16(ck + dst, zero);
+            st16(cv + dst, zero);
+        }
+    }
+}
+
+// =================================================================================================
+// decode_place: a chunk completed by decode steps goes to the ring and, unless sliding, behind the kept chunks
+// =================================================================================================
+struct PlaceParams {
+    const uint8_t* roles;                         // [BH]
+    uint8_t* ck; uint8_t* cv; uint8_t* valid;
+    long long* size_global; long long* size_local; int32_t* state;
+    int C, SW, Lcap, rowB, tail;
+};
+
+__global__ void __launch_bounds__(kCopyThreads) decode_place_kernel(const PlaceParams p) {
+    const int bh = blockIdx.x, tid = threadIdx.x;
+    const int vpt = p.rowB >> 4, tpp = kCopyThreads / vpt;
+    const int trow = tid / vpt, tvec = (tid % vpt) << 4;
+    uint8_t* ck = p.ck + (size_t)bh * p.Lcap * p.rowB;
+    uint8_t* cv = p.cv + (size_t)bh * p.Lcap * p.rowB;
+    uint8_t* valid = p.valid + (size_t)bh * p.Lcap;
+    const int role = p.roles[bh];
+    const int T0 = p.state[0];
+    const long long sg = p.size_global[bh], sl = p.size_local[bh];
+    const int len = (int)(sg + sl);
+    const uint4 zero = make_uint4(0, 0, 0, 0);
+    int dst, new_len;
+    long long nsg = sg, nsl = sl;
+    if (role == NATS_ROLE_GLOBAL) { dst = (int)sg; nsg = sg + p.C; nsl = 0; }
+    else if (role == NATS_ROLE_LOCAL) { dst = len; nsl = sl + p.C; }
+    else { dst = -1; }
+    new_len = (int)(nsg + nsl);
+    if (trow < tpp) {
+        for (int i = trow; i < p.C; i += tpp) {
+            const size_t src = (size_t)(T0 + i) * p.rowB + tvec;
+            const uint4 kk = ld16(ck + src), vv = ld16(cv + src);
+            const int slot = (p.tail + i) % p.SW;
+            const size_t rdst = (size_t)slot * p.rowB + tvec;
+            const bool sw = role == NATS_ROLE_SLIDING;
+            st16(ck + rdst, sw ? kk : zero);
+            st16(cv + rdst, sw ? vv : zero);
+            if (tvec == 0) valid[slot] = sw ? 1 : 0;
+            if (dst >= 0 && dst != T0) {
+                const size_t mdst = (size_t)(dst + i) * p.rowB + tvec;
+                st16(ck + mdst, kk);
+                st16(cv + mdst, vv);
+            }
+        }
+    }
+    __syncthreads();   // every read of the pending chunk is done before the region behind the new length is cleared
+    if (trow < tpp) {
+        const int end = min(T0 + p.C, p.Lcap);
+        for (int d = new_len + trow; d < end; d += tpp) {
+            const size_t o = (size_t)d * p.rowB + tvec;
+            st16(ck + o, zero);
+            st16(cv + o, zero);
+            if (tvec == 0) valid[d] = 0;
+        }
+        if (dst >= 0)
+            for (int i = trow; i < p.C; i += tpp)
+                if (tvec == 0) valid[dst + i] = 1;
+    }
+    if (tid == 0) {
+        p.size_global[bh] = nsg;
+        p.size_local[bh] = nsl;
+    }
+    publish_max_len(p.state, new_len, gridDim.x);
+}
+
+}  // namespace nats
+
+// =================================================================================================
+// C ABI
+// =================================================================================================
+using namespace nats;
+
+extern "C" __attribute__((visibility("default"))) const char* nats_b200_last_error(void) { return last_error_buf(); }
+
+extern "C" __attribute__((visibility("default"))) const char* nats_b200_build_info(void) {
+    return "libnats_b200 sm_100a; prefill tile 128x128 (tcgen05/TMEM/TMA), head_dim {64,128}, N <= 524288; "
+           "decode head_dim {64,128}, group size {1,2,4,8}";
+}
+
+static int check_common(int B, int Hkv, int N, int C, int SW) {
+    NATS_CHECK_ARG(B > 0 && Hkv > 0 && N > 0, "B, Hkv and N must be positive (got %d, %d, %d)", B, Hkv, N);
+    NATS_CHECK_ARG(C > 0 && SW > 0 && SW % C == 0, "sliding window %d must be a positive multiple of the chunk size %d", SW, C);
+    NATS_CHECK_ARG((long long)B * Hkv <= 65535, "B * Hkv = %lld exceeds the grid limit 65535", (long long)B * Hkv);
+    return NATS_OK;
+}
+
+extern "C" __attribute__((visibility("default"))) int nats_b200_role_prep(const uint8_t* d_roles, int B, int Hkv, int N, int C, int SW,
+                                   int32_t* d_lim, int32_t* d_tile_max, int32_t* d_tile_min, int64_t* d_kept_tiles,
+                                   void* stream) {
+    if (int rc = check_common(B, Hkv, N, C, SW)) return rc;
+    NATS_CHECK_ARG(d_roles && d_lim && d_tile_max && d_tile_min, "null pointer");
+    const int Nc = cdiv(N, C), Nt = cdiv(N, kTile);
+    role_prep_kernel<<<B * Hkv, kScanThreads, 0, (cudaStream_t)stream>>>(
+        d_roles, Nc, N, C, SW, Nt, d_lim, d_tile_max, d_tile_min, (long long*)d_kept_tiles);
+    NATS_CHECK_CUDA(cudaGetLastError());
+    return NATS_OK;
+}
+
+extern "C" __attribute__((visibility("default"))) int nats_b200_evict_plan(const uint8_t* d_roles, int B, int Hkv, int N, int C, int SW,
+                                    int32_t* d_rank, int64_t* d_size_global, int64_t* d_size_local, int32_t* d_state,
+                                    void* stream) {
+    if (int rc = check_common(B, Hkv, N, C, SW)) return rc;
+    NATS_CHECK_ARG(d_roles && d_rank && d_size_global && d_size_local && d_state, "null pointer");
+    const int Nc = cdiv(N, C);
+    evict_plan_kernel<<<B * Hkv, kScanThreads, 0, (cudaStream_t)stream>>>(
+        d_roles, Nc, N / C, C, SW, d_rank, (long long*)d_size_global, (long long*)d_size_local, d_state);
+    NATS_CHECK_CUDA(cudaGetLastError());
+    return NATS_OK;
+}
+
+static int check_row(int D) {
+    NATS_CHECK_ARG(D > 0 && (D * 2) % 16 == 0 && D <= 2048 && 256 % ((D * 2) / 16) == 0,
+                   "head_dim %d: a bf16 row must be a whole number of 16-byte vectors that divides 256", D);
+    return NATS_OK;
+}
+
+extern "C" __attribute__((visibility("default"))) int nats_b200_evict_compact(const void* d_k, const void* d_v, const uint8_t* d_roles, const int32_t* d_rank,
+                                       const int64_t* d_size_global, const int64_t* d_size_local, const int32_t* d_state,
+                                       int B, int Hkv, int N, int D, int C, int SW,
+                                       void* d_cache_k, void* d_cache_v, uint8_t* d_valid, int Lcap, void* stream) {
+    if (int rc = check_common(B, Hkv, N, C, SW)) return rc;
+    if (int rc = check_row(D)) return rc;
+    NATS_CHECK_ARG(d_k && d_v && d_roles && d_rank && d_size_global && d_size_local && d_state && d_cache_k && d_cache_v && d_valid,
+                   "null pointer");
+    NATS_CHECK_ARG(((uintptr_t)d_k | (uintptr_t)d_v | (uintptr_t)d_cache_k | (uintptr_t)d_cache_v) % 16 == 0,
+                   "K/V and cache pointers must be 16-byte aligned");
+    NATS_CHECK_ARG(Lcap >= SW + C, "cache capacity %d is smaller than ring + one chunk (%d)", Lcap, SW + C);
+    CompactParams p;
+    p.k = (const uint8_t*)d_k; p.v = (const uint8_t*)d_v; p.roles = d_roles; p.rank = d_rank;
+    p.size_global = (const long long*)d_size_global; p.size_local = (const long long*)d_size_local; p.state = d_state;
+    p.ck = (uint8_t*)d_cache_k; p.cv = (uint8_t*)d_cache_v; p.valid = d_valid;
+    p.N = N; p.Nc = cdiv(N, C); p.n_full = N / C; p.C = C; p.SW = SW; p.Lcap = Lcap; p.rowB = D * 2;
+    p.nA = cdiv(p.n_full * C, kTokPerBlock);
+    p.nB = cdiv(SW, kTokPerBlock);
+    const int nC = cdiv(Lcap - SW, kTokPerBlock);
+    dim3 grid(p.nA + p.nB + nC, B * Hkv);
+    evict_compact_kernel<<<grid, kCopyThreads, 0, (cudaStream_t)stream>>>(p);
+    NATS_CHECK_CUDA(cudaGetLastError());
+    return NATS_OK;
+}
+
+extern "C" __attribute__((visibility("default"))) int nats_b200_decode_place(const uint8_t* d_roles, void* d_cache_k, void* d_cache_v, uint8_t* d_valid, int Lcap,
+                                      int64_t* d_size_global, int64_t* d_size_local, int32_t* d_state,
+                                      int tail, int B, int Hkv, int D, int C, int SW, void* stream) {
+    if (int rc = check_common(B, Hkv, 1, C, SW)) return rc;
+    if (int rc = check_row(D)) return rc;
+    NATS_CHECK_ARG(d_roles && d_cache_k && d_cache_v && d_valid && d_size_global && d_size_local && d_state, "null pointer");
+    NATS_CHECK_ARG(tail >= 0 && tail < SW && tail % C == 0, "ring tail %d must be a chunk multiple inside the window %d", tail, SW);
+    PlaceParams p;
+    p.roles = d_roles; p.ck = (uint8_t*)d_cache_k; p.cv = (uint8_t*)d_cache_v; p.valid = d_valid;
+    p.size_global = (long long*)d_size_global; p.size_local = (long long*)d_size_local; p.state = d_state;
+    p.C = C; p.SW = SW; p.Lcap = Lcap; p.rowB = D * 2; p.tail = tail;
+    decode_place_kernel<<<B * Hkv, kCopyThreads, 0, (cudaStream_t)stream>>>(p);
+    NATS_CHECK_CUDA(cudaGetLastError());
+    return NATS_OK;
+}

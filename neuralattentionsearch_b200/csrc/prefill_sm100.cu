@@ -1,0 +1,620 @@
+// Role-masked chunked flash-attention prefill for sm_100a: TMA-fed tcgen05.mma with TMEM accumulators.
+//
+// One CTA = one 128-row query tile x one kv-head x up to two query heads of that kv-head's group.  The two heads
+// share every K/V tile that is loaded and keep the tensor pipe busy in turns: while the softmax warps of one head
+// work on S = Q.K^T in TMEM, the tensor core runs the other head's MMAs.
+//
+//   warp 0      TMA producer: Q (once), then K and V of every kept KV tile through 2-stage rings
+//   warp 1      MMA issuer (one elected lane): S_h = Q_h.K^T (SS), O_h += P_h.V (TS, P read from TMEM)
+//   warps 4-7   softmax of head slot 0: one thread per query row, S read with tcgen05.ld, online softmax in
+//   warps 8-11  softmax of head slot 1  registers, P written back over S as packed bf16 with tcgen05.st
+//
+// Which KV tiles are visited comes from the role bitmap: a list of kept tiles is built in shared memory from the
+// per-tile max / min row limits (nats_b200_role_prep); tiles without a visible entry are never loaded.  Only tiles
+// whose min limit does not cover the whole query tile (and the diagonal) pay for per-element masking.
+//
+// TMEM (512 columns): S0 [0,128) S1 [128,256) O0 [256,256+D) O1 [384,384+D); P_h aliases the first 64 columns of S_h.
+// Every mbarrier wait is bounded: on a time-out the CTA raises the caller's status word, drains and exits.
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace nats {
+
+constexpr int kPrefillThreads = 384;
+constexpr int kStages = 2;
+constexpr uint32_t kBoxBytes = 128 * 64 * 2;            // one TMA box: 128 rows x 64 bf16, 128-byte swizzled
+constexpr float kRescaleThreshold = 8.0f;               // log2 units: O is rescaled only when the row max grows by more
+constexpr unsigned long long kWaitLimitNs = 400ull * 1000ull * 1000ull;
+
+enum : int { kErrQ = 1, kErrKFull, kErrVFull, kErrKEmpty, kErrVEmpty, kErrSFull, kErrPFull, kErrOFull };
+
+struct PrefillParams {
+    __nv_bfloat16* o;                 // [B,Hq,N,D]
+    const int32_t* lim;               // [B,Hkv,Nc]
+    const int32_t* tile_max;          // [B,Hkv,Nt]
+    const int32_t* tile_min;
+    int32_t* status;
+    int Hq, Hkv, N, C, Nc, Nt, nrep, n_groups;   // n_groups = ceil(nrep / 2)
+    float scale_log2;
+};
+
+// ---- PTX wrappers -------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+// Bounded wait.  Returns false when the wait was given up (by this thread or, earlier, by another one of the CTA).
+// With abort_flag == nullptr only the time limit ends the wait (used to drain copies after the CTA has given up).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int32_t* status, int code) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long t0 = global_ns();
+#pragma unroll 1
+    for (uint32_t it = 0;; ++it) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((it & 63u) == 63u) {
+            if (abort_flag != nullptr && *abort_flag) return false;
+            if (global_ns() - t0 > kWaitLimitNs) {
+                if (abort_flag != nullptr) *abort_flag = 1;
+                atomicCAS(status, 0, code);
+                return false;
+            }
+        }
+    }
+}
+
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1), "r"(c2) : "memory");
+}
+__device__ __forceinline__ void prefetch_tmap(const CUtensorMap* map) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// D[tmem] (+)= A[smem desc] * B[smem desc]
+__device__ __forceinline__ void mma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// D[tmem] (+)= A[tmem] * B[smem desc]
+__device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+
+// 32 lanes x 32 consecutive 32-bit columns: thread i of the warp gets its lane's columns
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+        "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+        ::"r"(taddr),
+          "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+          "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+          "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+        ::"r"(taddr),
+          "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+}
+
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    uint32_t r;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+
+// ---- descriptors ----------------------------------------------------------------------------------
+// Shared-memory matrix descriptor of a 128-byte swizzled tile whose rows are 128 bytes (what one TMA box leaves):
+// start address >> 4 in [0,14), leading byte offset >> 4 in [16,30), stride byte offset >> 4 in [32,46),
+// descriptor version 1 in [46,48), swizzle mode 2 (128 B) in [61,64).
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    return (uint64_t)((addr & 0x3ffffu) >> 4) | ((uint64_t)(lbo_bytes >> 4) << 16) | ((uint64_t)(sbo_bytes >> 4) << 32) |
+           (1ull << 46) | (2ull << 61);
+}
+// Instruction descriptor, kind::f16: fp32 accumulate, bf16 A and B, A K-major, B K-major or MN-major, M = 128.
+__host__ __device__ constexpr uint32_t instr_desc(int n, bool b_mn_major) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((b_mn_major ? 1u : 0u) << 16) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+}
+
+// ---- shared memory --------------------------------------------------------------------------------
+template <int D>
+struct __align__(1024) PrefillSmem {
+    uint8_t q[2][128 * D * 2];             // one tile per head slot; D/64 boxes of 16 KB each
+    uint8_t k[kStages][128 * D * 2];
+    uint8_t v[kStages][128 * D * 2];
+    uint16_t list[kMaxTiles];              // kept KV tiles of this query tile, ascending; bit 15 = needs element masking
+    int seg_count[kMaxTiles / 32];
+    unsigned long long bar_q, bar_k_full[kStages], bar_k_empty[kStages], bar_v_full[kStages], bar_v_empty[kStages];
+    unsigned long long bar_s_full[2], bar_p_full[2], bar_o_full[2];
+    uint32_t tmem_base;
+    int n_kept;
+    int abort_flag;
+};
+
+template <int D>
+__global__ void __launch_bounds__(kPrefillThreads, 1)
+prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+               const __grid_constant__ CUtensorMap map_v, const PrefillParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    PrefillSmem<D>& sm = *reinterpret_cast<PrefillSmem<D>*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    constexpr int NBOX = D / 64;                       // TMA boxes per tile
+    constexpr uint32_t TILE_BYTES = NBOX * kBoxBytes;
+    constexpr uint32_t IDESC_QK = instr_desc(128, false);
+    constexpr uint32_t IDESC_PV = instr_desc(D, true);
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int t = p.Nt - 1 - (int)blockIdx.x;          // heavy (late) query tiles are scheduled first
+    const int grp = blockIdx.y % p.n_groups, hkv = blockIdx.y / p.n_groups, b = blockIdx.z;
+    const int bh = b * p.Hkv + hkv;
+    const int head0 = hkv * p.nrep + grp * 2;          // query head of slot 0
+    const int nslots = min(2, p.nrep - grp * 2);
+    const int q_lo = t * kTile;
+    const int q_hi = min(q_lo + kTile, p.N) - 1;
+    volatile int* abort_flag = &sm.abort_flag;
+
+    if (tid == 0) sm.abort_flag = (*reinterpret_cast<volatile int32_t*>(p.status) != 0);
+    __syncthreads();
+    if (sm.abort_flag) return;                         // an earlier CTA gave up: do not start (uniform for the CTA)
+
+    // ---- set-up: barriers, TMEM, Q load ----
+    if (tid == 0) {
+        mbar_init(smem_u32(&sm.bar_q), 1);
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(smem_u32(&sm.bar_k_full[s]), 1);
+            mbar_init(smem_u32(&sm.bar_k_empty[s]), 1);
+            mbar_init(smem_u32(&sm.bar_v_full[s]), 1);
+            mbar_init(smem_u32(&sm.bar_v_empty[s]), 1);
+        }
+        for (int h = 0; h < 2; ++h) {
+            mbar_init(smem_u32(&sm.bar_s_full[h]), 1);
+            mbar_init(smem_u32(&sm.bar_p_full[h]), 128);
+            mbar_init(smem_u32(&sm.bar_o_full[h]), 1);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        prefetch_tmap(&map_q);
+        prefetch_tmap(&map_k);
+        prefetch_tmap(&map_v);
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(&sm.tmem_base), 512);
+        tmem_relinquish();
+        tc_fence_before();
+    }
+    __syncthreads();
+    if (tid == 0) {
+        mbar_expect_tx(smem_u32(&sm.bar_q), nslots * TILE_BYTES);
+        for (int h = 0; h < nslots; ++h)
+            for (int x = 0; x < NBOX; ++x)
+                tma_load_3d(smem_u32(&sm.q[h][x * kBoxBytes]), &map_q, smem_u32(&sm.bar_q), x * 64, q_lo, b * p.Hq + head0 + h);
+    }
+
+    // ---- kept-tile list: ordered compaction of the tiles 0..t that hold a visible entry ----
+    {
+        const int32_t* tmax = p.tile_max + (size_t)bh * p.Nt;
+        const int32_t* tmin = p.tile_min + (size_t)bh * p.Nt;
+        const int nseg = (t + 32) / 32;                // tiles 0..t in segments of 32
+        constexpr int NW = kPrefillThreads / 32;
+        for (int s = warp; s < nseg; s += NW) {
+            const int kt = s * 32 + lane;
+            const bool keep = kt <= t && tmax[kt] >= q_lo;
+            const unsigned m = __ballot_sync(0xffffffffu, keep);
+            if (lane == 0) sm.seg_count[s] = __popc(m);
+        }
+        __syncthreads();
+        if (warp == 0) {                               // exclusive scan of the segment counts
+            int carry = 0;
+            for (int s0 = 0; s0 < nseg; s0 += 32) {
+                const int s = s0 + lane;
+                const int c = s < nseg ? sm.seg_count[s] : 0;
+                const int inc = warp_incl_scan(c, lane);
+                if (s < nseg) sm.seg_count[s] = carry + inc - c;
+                carry += __shfl_sync(0xffffffffu, inc, 31);
+            }
+            if (lane == 0) sm.n_kept = carry;
+        }
+        __syncthreads();
+        for (int s = warp; s < nseg; s += NW) {
+            const int kt = s * 32 + lane;
+            const bool keep = kt <= t && tmax[kt] >= q_lo;
+            const unsigned m = __ballot_sync(0xffffffffu, keep);
+            if (keep) {
+                const bool partial = kt == t || tmin[kt] < q_hi;
+                sm.list[sm.seg_count[s] + __popc(m & ((1u << lane) - 1u))] = (uint16_t)(kt | (partial ? 0x8000 : 0));
+            }
+        }
+        __syncthreads();
+    }
+    const int n_kept = sm.n_kept;
+    tc_fence_after();
+    const uint32_t tmem = sm.tmem_base;
+
+    if (warp == 0) {
+        // =============================== TMA producer ===============================
+        int issued_k = 0, issued_v = 0;
+        bool ok = true;
+        for (int jt = 0; jt < n_kept && ok; ++jt) {
+            const int kt = sm.list[jt] & 0x7fff;
+            const int s = jt % kStages;
+            const uint32_t ph = (jt / kStages) & 1;
+            if (jt >= kStages) ok = mbar_wait(smem_u32(&sm.bar_k_empty[s]), ph ^ 1, abort_flag, p.status, kErrKEmpty);
+            if (!ok) break;
+            if (lane == 0) {
+                mbar_expect_tx(smem_u32(&sm.bar_k_full[s]), TILE_BYTES);
+                for (int x = 0; x < NBOX; ++x)
+                    tma_load_3d(smem_u32(&sm.k[s][x * kBoxBytes]), &map_k, smem_u32(&sm.bar_k_full[s]), x * 64, kt * kTile, bh);
+            }
+            ++issued_k;
+            if (jt >= kStages) ok = mbar_wait(smem_u32(&sm.bar_v_empty[s]), ph ^ 1, abort_flag, p.status, kErrVEmpty);
+            if (!ok) break;
+            if (lane == 0) {
+                mbar_expect_tx(smem_u32(&sm.bar_v_full[s]), TILE_BYTES);
+                for (int x = 0; x < NBOX; ++x)
+                    tma_load_3d(smem_u32(&sm.v[s][x * kBoxBytes]), &map_v, smem_u32(&sm.bar_v_full[s]), x * 64, kt * kTile, bh);
+            }
+            ++issued_v;
+            __syncwarp();
+        }
+        if (!ok) {
+            // given up: let copies that are still in flight land before the shared memory is released
+            for (int jt = max(0, issued_k - kStages); jt < issued_k; ++jt)
+                mbar_wait(smem_u32(&sm.bar_k_full[jt % kStages]), (jt / kStages) & 1, nullptr, p.status, kErrKFull);
+            for (int jt = max(0, issued_v - kStages); jt < issued_v; ++jt)
+                mbar_wait(smem_u32(&sm.bar_v_full[jt % kStages]), (jt / kStages) & 1, nullptr, p.status, kErrVFull);
+        }
+    } else if (warp == 1) {
+        // =============================== MMA issuer ===============================
+        bool ok = mbar_wait(smem_u32(&sm.bar_q), 0, abort_flag, p.status, kErrQ);
+        auto issue_qk = [&](int h, int s) {
+            // S_h[128 x 128] = Q_h[128 x D] . K[128 x D]^T : D/16 MMAs of K = 16
+            const uint32_t qa = smem_u32(&sm.q[h][0]), ka = smem_u32(&sm.k[s][0]);
+#pragma unroll
+            for (int ks = 0; ks < D / 16; ++ks) {
+                const uint32_t off = (ks / 4) * kBoxBytes + (ks % 4) * 32;
+                mma_ss(tmem + h * 128, smem_desc(qa + off, 16, 1024), smem_desc(ka + off, 16, 1024), IDESC_QK, ks > 0);
+            }
+        };
+        auto issue_pv = [&](int h, int s, bool first) {
+            // O_h[128 x D] (+)= P_h[128 x 128] . V[128 x D] : 8 MMAs of K = 16; V is MN-major (D contiguous)
+            const uint32_t va = smem_u32(&sm.v[s][0]);
+#pragma unroll
+            for (int ks = 0; ks < 8; ++ks)
+                mma_ts(tmem + 256 + h * 128, tmem + h * 128 + ks * 8, smem_desc(va + ks * 2048, kBoxBytes, 1024), IDESC_PV,
+                       (first && ks == 0) ? 0u : 1u);
+        };
+        if (ok && n_kept > 0) {
+            ok = mbar_wait(smem_u32(&sm.bar_k_full[0]), 0, abort_flag, p.status, kErrKFull);
+            if (ok) {
+                tc_fence_after();
+                if (lane == 0) {
+                    for (int h = 0; h < nslots; ++h) {
+                        issue_qk(h, 0);
+                        tc_commit(smem_u32(&sm.bar_s_full[h]));
+                    }
+                    tc_commit(smem_u32(&sm.bar_k_empty[0]));
+                }
+                __syncwarp();
+            }
+        }
+        for (int jt = 0; jt < n_kept && ok; ++jt) {
+            const int s = jt % kStages;
+            const uint32_t ph = (jt / kStages) & 1;
+            const bool has_next = jt + 1 < n_kept;
+            const int sn = (jt + 1) % kStages;
+            const uint32_t phn = ((jt + 1) / kStages) & 1;
+            ok = mbar_wait(smem_u32(&sm.bar_v_full[s]), ph, abort_flag, p.status, kErrVFull);
+            for (int h = 0; h < nslots && ok; ++h) {
+                ok = mbar_wait(smem_u32(&sm.bar_p_full[h]), jt & 1, abort_flag, p.status, kErrPFull);
+                if (ok && has_next && h == 0) ok = mbar_wait(smem_u32(&sm.bar_k_full[sn]), phn, abort_flag, p.status, kErrKFull);
+                if (!ok) break;
+                tc_fence_after();
+                if (lane == 0) {
+                    issue_pv(h, s, jt == 0);
+                    if (!has_next) tc_commit(smem_u32(&sm.bar_o_full[h]));
+                    if (h == nslots - 1) tc_commit(smem_u32(&sm.bar_v_empty[s]));
+                    if (has_next) {
+                        issue_qk(h, sn);
+                        tc_commit(smem_u32(&sm.bar_s_full[h]));
+                        if (h == nslots - 1) tc_commit(smem_u32(&sm.bar_k_empty[sn]));
+                    }
+                }
+                __syncwarp();
+            }
+        }
+    } else if (warp >= 4 && warp < 4 + 4 * nslots) {
+        // =============================== softmax + epilogue ===============================
+        const int h = (warp - 4) / 4;                    // head slot
+        const int row = (warp & 3) * 32 + lane;          // query row inside the tile == TMEM lane
+        const int qi = q_lo + row;                       // query token index
+        const uint32_t lane_addr = ((uint32_t)((warp & 3) * 32)) << 16;
+        const uint32_t tS = tmem + lane_addr + h * 128;
+        const uint32_t tO = tmem + lane_addr + 256 + h * 128;
+        const int32_t* lim = p.lim + (size_t)bh * p.Nc;
+        const float scale = p.scale_log2;
+        float m_ref = -INFINITY, l_sum = 0.f;
+        bool ok = true;
+        for (int jt = 0; jt < n_kept; ++jt) {
+            const int entry = sm.list[jt];
+            const int kt = entry & 0x7fff;
+            const bool partial = (entry & 0x8000) != 0;
+            ok = mbar_wait(smem_u32(&sm.bar_s_full[h]), jt & 1, abort_flag, p.status, kErrSFull);
+            if (!ok) break;
+            tc_fence_after();
+            // pass 1: row maximum of the visible scores
+            float mx = -INFINITY;
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+                uint32_t r[32];
+                tmem_ld32(tS + c * 32, r);
+                tc_wait_ld();
+                if (partial) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        const int kj = kt * kTile + c * 32 + i;
+                        const bool vis = kj <= qi && (kj < p.N) && qi <= lim[kj / p.C];
+                        if (vis) mx = fmaxf(mx, __uint_as_float(r[i]));
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
+                }
+            }
+            mx *= scale;                                    // scale > 0
+            // online softmax with lazy rescaling: the reference maximum only moves when the row max grew by > threshold
+            float alpha = 1.f;
+            bool need = false;
+            if (mx > m_ref + kRescaleThreshold) {           // also true for the first visible tile (m_ref = -inf)
+                if (m_ref != -INFINITY) {                   // a row without visible entries so far has O = 0, l = 0
+                    alpha = ex2(m_ref - mx);
+                    l_sum *= alpha;
+                    need = true;
+                }
+                m_ref = mx;
+            }
+            if (jt > 0 && __any_sync(0xffffffffu, need)) {
+                // O_h of the previous tiles is complete (the commit behind S_h covers every earlier MMA): rescale it
+#pragma unroll 1
+                for (int c = 0; c < D / 32; ++c) {
+                    uint32_t r[32];
+                    tmem_ld32(tO + c * 32, r);
+                    tc_wait_ld();
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+                    tmem_st32(tO + c * 32, r);
+                }
+            }
+            const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
+            // pass 2: P = exp2(S * scale - m), row sum in fp32, P packed to bf16 over the first 64 columns of S_h
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+                uint32_t r[32];
+                tmem_ld32(tS + c * 32, r);
+                tc_wait_ld();
+                uint32_t pk[16];
+                float ls = 0.f;
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    float p0 = ex2(fmaf(__uint_as_float(r[i]), scale, -m_use));
+                    float p1 = ex2(fmaf(__uint_as_float(r[i + 1]), scale, -m_use));
+                    if (partial) {
+                        const int kj = kt * kTile + c * 32 + i;
+                        const bool v0 = kj <= qi && (kj < p.N) && qi <= lim[kj / p.C];
+                        const bool v1 = (kj + 1) <= qi && (kj + 1 < p.N) && qi <= lim[(kj + 1) / p.C];
+                        p0 = v0 ? p0 : 0.f;
+                        p1 = v1 ? p1 : 0.f;
+                    }
+                    ls += p0 + p1;
+                    pk[i / 2] = pack_bf16(p0, p1);
+                }
+                l_sum += ls;
+                tmem_st16(tS + c * 16, pk);
+            }
+            tc_wait_st();
+            tc_fence_before();
+            mbar_arrive(smem_u32(&sm.bar_p_full[h]));
+        }
+        // epilogue: O / l -> bf16 -> global
+        if (ok && n_kept > 0) ok = mbar_wait(smem_u32(&sm.bar_o_full[h]), 0, abort_flag, p.status, kErrOFull);
+        if (ok && n_kept > 0) {
+            tc_fence_after();
+            const float inv = l_sum > 0.f ? 1.f / l_sum : 0.f;
+            __nv_bfloat16* orow = p.o + (((size_t)b * p.Hq + head0 + h) * p.N + qi) * D;
+#pragma unroll 1
+            for (int c = 0; c < D / 32; ++c) {
+                uint32_t r[32];
+                tmem_ld32(tO + c * 32, r);
+                tc_wait_ld();
+                if (qi < p.N) {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 8) {
+                        uint4 w;
+                        w.x = pack_bf16(__uint_as_float(r[i]) * inv, __uint_as_float(r[i + 1]) * inv);
+                        w.y = pack_bf16(__uint_as_float(r[i + 2]) * inv, __uint_as_float(r[i + 3]) * inv);
+                        w.z = pack_bf16(__uint_as_float(r[i + 4]) * inv, __uint_as_float(r[i + 5]) * inv);
+                        w.w = pack_bf16(__uint_as_float(r[i + 6]) * inv, __uint_as_float(r[i + 7]) * inv);
+                        st16(orow + c * 32 + i, w);
+                    }
+                }
+            }
+        }
+    }
+    // ---- teardown ----
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        if (sm.abort_flag) {
+            // MMAs may still be running: give them time before the accumulator columns are released
+            const unsigned long long t0 = global_ns();
+            while (global_ns() - t0 < 200000ull) {}
+        }
+        tc_fence_after();
+        tmem_dealloc(tmem, 512);
+    }
+}
+
+// ---- host side ------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (fn) return fn;
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) != cudaSuccess ||
+        qres != cudaDriverEntryPointSuccess)
+        return nullptr;
+    fn = (EncodeTiledFn)ptr;
+    return fn;
+}
+
+// [heads, N, D] bf16 viewed as a 3-D tensor (D innermost); box = 64 x 128 x 1 with 128-byte swizzle; rows past N read zero
+static int make_map(CUtensorMap* map, const void* base, int heads, int N, int D) {
+    EncodeTiledFn fn = get_encode_fn();
+    if (!fn) return fail(NATS_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+    cuuint64_t dims[3] = {(cuuint64_t)D, (cuuint64_t)N, (cuuint64_t)heads};
+    cuuint64_t strides[2] = {(cuuint64_t)D * 2, (cuuint64_t)N * D * 2};
+    cuuint32_t box[3] = {64, 128, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(NATS_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+    return NATS_OK;
+}
+
+struct PrefillWs { size_t lim, tmax, tmin, total; };
+static PrefillWs prefill_ws(int B, int Hkv, int N, int C) {
+    PrefillWs w;
+    const size_t Nc = cdiv(N, C), Nt = cdiv(N, kTile);
+    w.lim = 0;
+    w.tmax = align_up((size_t)B * Hkv * Nc * 4, 256);
+    w.tmin = w.tmax + align_up((size_t)B * Hkv * Nt * 4, 256);
+    w.total = w.tmin + align_up((size_t)B * Hkv * Nt * 4, 256);
+    return w;
+}
+
+template <int D>
+static int launch_prefill(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const PrefillParams& p,
+                          int B, cudaStream_t st) {
+    const size_t smem = sizeof(PrefillSmem<D>) + 1024;
+    static bool attr_set = false;
+    if (!attr_set) {
+        NATS_CHECK_CUDA(cudaFuncSetAttribute(prefill_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        attr_set = true;
+    }
+    dim3 grid(p.Nt, p.Hkv * p.n_groups, B);
+    prefill_kernel<D><<<grid, kPrefillThreads, smem, st>>>(mq, mk, mv, p);
+    NATS_CHECK_CUDA(cudaGetLastError());
+    return NATS_OK;
+}
+
+}  // namespace nats
+
+using namespace nats;
+
+extern "C" __attribute__((visibility("default"))) size_t nats_b200_prefill_workspace_bytes(int B, int Hkv, int N, int C) {
+    if (B <= 0 || Hkv <= 0 || N <= 0 || C <= 0) return 0;
+    return prefill_ws(B, Hkv, N, C).total;
+}
+
+extern "C" __attribute__((visibility("default"))) int nats_b200_prefill_fwd(const void* d_q, const void* d_k, const void* d_v, void* d_o, const uint8_t* d_roles,
+                                     int B, int Hq, int Hkv, int N, int D, int C, int SW, float sm_scale,
+                                     void* d_workspace, size_t workspace_bytes, int64_t* d_kept_tiles, int32_t* d_status,
+                                     void* stream) {
+    NATS_CHECK_ARG(B > 0 && Hq > 0 && Hkv > 0 && N > 0 && Hq % Hkv == 0, "bad shape B=%d Hq=%d Hkv=%d N=%d", B, Hq, Hkv, N);
+    NATS_CHECK_ARG(C > 0 && SW > 0 && SW % C == 0, "sliding window %d must be a positive multiple of the chunk size %d", SW, C);
+    NATS_CHECK_ARG(d_q && d_k && d_v && d_o && d_roles && d_workspace && d_status, "null pointer");
+    NATS_CHECK_ARG(((uintptr_t)d_q | (uintptr_t)d_k | (uintptr_t)d_v | (uintptr_t)d_o | (uintptr_t)d_workspace) % 16 == 0,
+                   "q, k, v, o and the workspace must be 16-byte aligned");
+    NATS_CHECK_ARG(sm_scale > 0.f, "sm_scale must be positive");
+    if (D != 64 && D != 128) return fail(NATS_ERR_UNSUPPORTED, "prefill supports head_dim 64 and 128, got %d", D);
+    NATS_CHECK_ARG(N <= kMaxTiles * kTile, "N = %d exceeds the prefill limit %d", N, kMaxTiles * kTile);
+    NATS_CHECK_ARG((long long)B <= 65535 && (long long)Hkv * ((Hq / Hkv + 1) / 2) <= 65535, "grid too large");
+    const PrefillWs w = prefill_ws(B, Hkv, N, C);
+    if (workspace_bytes < w.total)
+        return fail(NATS_ERR_WORKSPACE, "prefill workspace: %zu bytes given, %zu needed", workspace_bytes, w.total);
+    uint8_t* ws = (uint8_t*)d_workspace;
+    int32_t* lim = (int32_t*)(ws + w.lim);
+    int32_t* tmax = (int32_t*)(ws + w.tmax);
+    int32_t* tmin = (int32_t*)(ws + w.tmin);
+    if (int rc = nats_b200_role_prep(d_roles, B, Hkv, N, C, SW, lim, tmax, tmin, d_kept_tiles, stream)) return rc;
+    CUtensorMap mq, mk, mv;
+    if (int rc = make_map(&mq, d_q, B * Hq, N, D)) return rc;
+    if (int rc = make_map(&mk, d_k, B * Hkv, N, D)) return rc;
+    if (int rc = make_map(&mv, d_v, B * Hkv, N, D)) return rc;
+    PrefillParams p;
+    p.o = (__nv_bfloat16*)d_o; p.lim = lim; p.tile_max = tmax; p.tile_min = tmin; p.status = d_status;
+    p.Hq = Hq; p.Hkv = Hkv; p.N = N; p.C = C; p.Nc = cdiv(N, C); p.Nt = cdiv(N, kTile);
+    p.nrep = Hq / Hkv; p.n_groups = (p.nrep + 1) / 2;
+    p.scale_log2 = sm_scale * 1.4426950408889634f;
+    if (D == 64) return launch_prefill<64>(mq, mk, mv, p, B, (cudaStream_t)stream);
+    return launch_prefill<128>(mq, mk, mv, p, B, (cudaStream_t)stream);
+}

@@ -1,0 +1,218 @@
+"""Functional entry points of the NAtS attention hot path on B200.
+
+The first three functions keep the names, argument meaning and return conventions of the reference's Triton
+entry points, so a caller can switch the import and nothing else:
+
+* ``nats_prefill``          src/nats/models/transformer/triton/nats_flashattn_fwd.py:617-725
+* ``nats_chunk_attention``  src/nats/models/transformer/triton/nats_chunk_attention.py:1154-1185   (forward only)
+* ``nats_attention``        src/nats/models/transformer/triton/flashattention_mask_on_chip.py:1018-1048 (forward only)
+
+All of them run the same kernel (``nats_b200_prefill_fwd``): the role mask is the one of the reference's eager
+path (``NAtSChunkLayerCache.generate_mask``), which the reference's own test treats as ground truth.  The lower
+part of the file wraps the remaining C-ABI entry points for the cache classes.  Nothing here computes attention
+with PyTorch ops: if the CUDA library is missing the import of ``_lib`` raises.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from . import _lib
+
+ROLE_GLOBAL, ROLE_LOCAL, ROLE_SLIDING = 0, 1, 2
+PREFILL_HEAD_DIMS = (64, 128)
+
+_status: dict[int, torch.Tensor] = {}
+_workspaces: dict[tuple, torch.Tensor] = {}
+
+
+def _p(t: torch.Tensor | None) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+def _stream(device: torch.device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def _need_cuda(*tensors: torch.Tensor) -> torch.device:
+    dev = tensors[0].device
+    for t in tensors:
+        if not t.is_cuda:
+            raise _lib.NatsB200Error('the NAtS B200 kernels need CUDA tensors; there is no CPU path')
+        if t.device != dev:
+            raise ValueError('all tensors must live on the same device')
+    return dev
+
+
+def status_word(device: torch.device) -> torch.Tensor:
+    """Per-device int32 word the prefill kernel raises when one of its bounded waits gives up."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    if idx not in _status:
+        _status[idx] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _status[idx]
+
+
+def check_status(device: torch.device | None = None) -> None:
+    """Synchronises with the device and raises if a kernel reported a timed-out wait since the last check."""
+    device = torch.device('cuda', torch.cuda.current_device()) if device is None else device
+    word = status_word(device)
+    code = int(word.item())
+    if code != 0:
+        word.zero_()
+        raise _lib.NatsB200Error(f'nats_b200_prefill_fwd gave up a bounded wait (code {code}); its output is invalid')
+
+
+def _workspace(kind: str, device: torch.device, nbytes: int, zero: bool = False) -> torch.Tensor:
+    key = (kind, device.index, torch.cuda.current_stream(device).cuda_stream)
+    ws = _workspaces.get(key)
+    if ws is None or ws.numel() < nbytes:
+        ws = (torch.zeros if zero else torch.empty)(max(nbytes, 256), dtype=torch.uint8, device=device)
+        _workspaces[key] = ws
+    return ws
+
+
+def roles_from_token_states_info(token_states_info: torch.Tensor) -> torch.Tensor:
+    """uint8 role codes [B,Hkv,Nc] from the one-hot ``token_states_info`` [B,Hkv,Nc,3] (first max wins)."""
+    if token_states_info.dtype == torch.uint8 and token_states_info.dim() == 3:
+        return token_states_info.contiguous()
+    return token_states_info.argmax(-1).to(torch.uint8).contiguous()
+
+
+def roles_from_end_seqs(end_seqs_idx: torch.Tensor, sliding_tokens: torch.Tensor) -> torch.Tensor:
+    """Role codes from what the Triton entry points take: ``end_seqs_idx[c] == c`` marks a global chunk
+    (nats_flashattn_fwd.py:96) and ``sliding_tokens`` a sliding one; everything else is local."""
+    nc = end_seqs_idx.shape[-1]
+    ar = torch.arange(nc, device=end_seqs_idx.device)
+    roles = torch.full(end_seqs_idx.shape, ROLE_LOCAL, dtype=torch.uint8, device=end_seqs_idx.device)
+    roles[end_seqs_idx == ar] = ROLE_GLOBAL
+    roles[sliding_tokens.to(torch.bool)] = ROLE_SLIDING
+    return roles.contiguous()
+
+
+def _as_bf16(t: torch.Tensor) -> torch.Tensor:
+    return t.to(torch.bfloat16).contiguous()
+
+
+def prefill_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, roles: torch.Tensor, chunk_size: int,
+                      sliding_window: int, sm_scale: float | None = None,
+                      kept_tiles: torch.Tensor | None = None) -> torch.Tensor:
+    """Role-masked causal attention of a first prefill call.  q [B,Hq,N,D], k/v [B,Hkv,N,D] (cast to bf16 if
+    needed), roles uint8 [B,Hkv,ceil(N/C)].  Returns o [B,Hq,N,D] in q's dtype."""
+    dev = _need_cuda(q, k, v, roles)
+    B, Hq, N, D = q.shape
+    Hkv = k.shape[1]
+    if k.shape != (B, Hkv, N, D) or v.shape != k.shape:
+        raise ValueError(f'k/v shape {tuple(k.shape)}/{tuple(v.shape)} does not match q {tuple(q.shape)}')
+    nc = -(-N // chunk_size)
+    if roles.shape != (B, Hkv, nc) or roles.dtype != torch.uint8:
+        raise ValueError(f'roles must be uint8 [{B},{Hkv},{nc}], got {roles.dtype} {tuple(roles.shape)}')
+    qb, kb, vb = _as_bf16(q), _as_bf16(k), _as_bf16(v)
+    o = torch.empty_like(qb)
+    lib = _lib.lib()
+    nbytes = lib.nats_b200_prefill_workspace_bytes(B, Hkv, N, chunk_size)
+    ws = _workspace('prefill', dev, nbytes)
+    scale = (1.0 / math.sqrt(D)) if sm_scale is None else float(sm_scale)
+    _lib.call('nats_b200_prefill_fwd', _p(qb), _p(kb), _p(vb), _p(o), _p(roles.contiguous()), B, Hq, Hkv, N, D,
+              chunk_size, sliding_window, scale, _p(ws), ws.numel(), _p(kept_tiles), _p(status_word(dev)), _stream(dev))
+    return o if q.dtype == torch.bfloat16 else o.to(q.dtype)
+
+
+def dense_role_mask(roles: torch.Tensor, chunk_size: int, sliding_window: int, n: int) -> torch.Tensor:
+    """bool [B,Hkv,N,N] visibility mask, materialised (debugging aid and the ``return_masks`` option; it is never
+    used to compute attention)."""
+    dev = roles.device
+    B, H, nc = roles.shape
+    lim = torch.empty(B, H, nc, dtype=torch.int32, device=dev)
+    nt = -(-n // 128)
+    tmax = torch.empty(B, H, nt, dtype=torch.int32, device=dev)
+    tmin = torch.empty_like(tmax)
+    _lib.call('nats_b200_role_prep', _p(roles.contiguous()), B, H, n, chunk_size, sliding_window, _p(lim), _p(tmax), _p(tmin),
+              None, _stream(dev))
+    lim_tok = lim.repeat_interleave(chunk_size, -1)[..., :n].long()
+    ar = torch.arange(n, device=dev)
+    return (ar[:, None] >= ar[None, :])[None, None] & (ar[None, None, :, None] <= lim_tok[:, :, None, :])
+
+
+# ------------------------------------------------------------------------------------------------
+# reference-named entry points
+# ------------------------------------------------------------------------------------------------
+def nats_prefill(q, k, v, end_seqs_idx, sliding_tokens, sm_scale,
+                 nats_chunk_size: int = 1,
+                 global_kv_size=None, local_kv_size=None, valid_sw_tokens=None, n_ctx_data=None, sw_token_tails=None,
+                 n_rep: int = 1, n_tokens_in_first_chunk: int = 0, local_seq_max_length: int = 4,
+                 return_masks: bool = False, block_n: int = 32):
+    """Drop-in for the reference's ``nats_prefill``: returns ``(o, mask_or_None)``.
+
+    ``block_n`` is accepted and ignored (the tile shape is fixed by the tensor-core kernel).  Attention over an
+    existing compacted cache (``global_kv_size`` given) is not built yet and raises ``NotImplementedError``."""
+    if global_kv_size is not None:
+        raise NotImplementedError('prefill continuation over an existing compacted cache is not built yet')
+    assert q.shape[-1] == k.shape[-1] == v.shape[-1]
+    assert q.shape[-1] in {16, 32, 64, 128, 256}
+    assert k.shape[2] == q.shape[2]
+    assert q.shape[1] == k.shape[1] * n_rep
+    roles = roles_from_end_seqs(end_seqs_idx, sliding_tokens)
+    o = prefill_attention(q, k, v, roles, nats_chunk_size, local_seq_max_length, sm_scale)
+    mask = dense_role_mask(roles, nats_chunk_size, local_seq_max_length, q.shape[2]) if return_masks else None
+    return o, mask
+
+
+def nats_chunk_attention(q, k, v, seq_info, end_seqs_idx, causal, sm_scale, nats_chunk_size: int,
+                         n_rep: int = 1, sparse_regularized_value: float = 0., local_seq_max_length: int = 4,
+                         compress_on_q: bool = True):
+    """Forward of the reference's chunked training attention (no autograd: inference build).  ``seq_info`` is the
+    one-hot role tensor [B,Hkv,Nc,3]; returns ``o`` shaped like ``q``."""
+    assert causal, 'only causal attention exists on this path'
+    roles = roles_from_token_states_info(seq_info)
+    return prefill_attention(q, k, v, roles, nats_chunk_size, local_seq_max_length, sm_scale)
+
+
+def nats_attention(q, k, v, seq_info, end_seqs_idx, causal, sm_scale, n_rep: int = 1,
+                   sparse_regularized_value: float = 0., local_seq_max_length: int = 4):
+    """Token-granular variant (chunk size 1) of ``nats_chunk_attention``."""
+    assert causal, 'only causal attention exists on this path'
+    roles = roles_from_token_states_info(seq_info)
+    return prefill_attention(q, k, v, roles, 1, local_seq_max_length, sm_scale)
+
+
+# ------------------------------------------------------------------------------------------------
+# thin wrappers of the cache entry points (used by cache.py)
+# ------------------------------------------------------------------------------------------------
+def evict_plan(roles: torch.Tensor, n: int, chunk_size: int, sliding_window: int, rank: torch.Tensor,
+               size_global: torch.Tensor, size_local: torch.Tensor, state: torch.Tensor) -> None:
+    B, H, _ = roles.shape
+    _lib.call('nats_b200_evict_plan', _p(roles), B, H, n, chunk_size, sliding_window, _p(rank), _p(size_global),
+              _p(size_local), _p(state), _stream(roles.device))
+
+
+def evict_compact(k: torch.Tensor, v: torch.Tensor, roles: torch.Tensor, rank: torch.Tensor, size_global: torch.Tensor,
+                  size_local: torch.Tensor, state: torch.Tensor, chunk_size: int, sliding_window: int,
+                  cache_k: torch.Tensor, cache_v: torch.Tensor, valid: torch.Tensor) -> None:
+    B, H, N, D = k.shape
+    _lib.call('nats_b200_evict_compact', _p(k), _p(v), _p(roles), _p(rank), _p(size_global), _p(size_local), _p(state),
+              B, H, N, D, chunk_size, sliding_window, _p(cache_k), _p(cache_v), _p(valid), cache_k.shape[2],
+              _stream(k.device))
+
+
+def decode_workspace_bytes(B: int, Hq: int, Hkv: int, D: int, max_len: int) -> int:
+    return _lib.lib().nats_b200_decode_workspace_bytes(B, Hq, Hkv, D, max_len)
+
+
+def decode_fwd(q: torch.Tensor, k_new: torch.Tensor, v_new: torch.Tensor, o: torch.Tensor, cache_k: torch.Tensor,
+               cache_v: torch.Tensor, valid: torch.Tensor, size_global: torch.Tensor, size_local: torch.Tensor,
+               state: torch.Tensor, fill: int, max_len_bound: int, chunk_size: int, sliding_window: int,
+               sm_scale: float, workspace: torch.Tensor) -> None:
+    B, Hq, _, D = q.shape
+    Hkv = k_new.shape[1]
+    _lib.call('nats_b200_decode_fwd', _p(q), _p(k_new), _p(v_new), _p(o), _p(cache_k), _p(cache_v), _p(valid),
+              cache_k.shape[2], _p(size_global), _p(size_local), _p(state), fill, max_len_bound, B, Hq, Hkv, D,
+              chunk_size, sliding_window, float(sm_scale), _p(workspace), workspace.numel(), _stream(q.device))
+
+
+def decode_place(roles: torch.Tensor, cache_k: torch.Tensor, cache_v: torch.Tensor, valid: torch.Tensor,
+                 size_global: torch.Tensor, size_local: torch.Tensor, state: torch.Tensor, tail: int, chunk_size: int,
+                 sliding_window: int) -> None:
+    B, H, _, D = cache_k.shape
+    _lib.call('nats_b200_decode_place', _p(roles), _p(cache_k), _p(cache_v), _p(valid), cache_k.shape[2], _p(size_global),
+              _p(size_local), _p(state), tail, B, H, D, chunk_size, sliding_window, _stream(cache_k.device))
