@@ -239,7 +239,13 @@ def main():
     ap.add_argument('--impl', default='b200', choices=['b200', 'reference'])
     ap.add_argument('--no-cpu', action='store_true', help='skip the CPU baseline leg')
     ap.add_argument('--no-decode', action='store_true', help='skip the decode leg')
+    ap.add_argument('--case', default='full', choices=['full', 'small'],
+                    help="'small' = a quarter of the heads / of the decode batch: the profiling case (inputs still exceed L2); "
+                         "its line is marked and is not a benchmark value")
     args = ap.parse_args()
+    if args.case == 'small':
+        WORKLOAD.update(Hq=8, Hkv=2)
+        DECODE.update(B=16)
 
     rank = int(os.environ.get('RANK', 0))
     world = int(os.environ.get('WORLD_SIZE', 1))
@@ -248,6 +254,9 @@ def main():
     config = dict(workload='prefill 32k + eviction: B1 x 32q/8kv heads, head_dim 128, N 32768, window 1024, chunk 128, '
                            'roles 5/15/80 % global/local/sliding; one sequence per GPU',
                   l2='inputs larger than L2 (q+k+v+o = 671 MB per step)', sharding='batch x kv-head, no data-path collective')
+    if args.case == 'small':
+        config = dict(config, workload='PROFILING CASE (not a benchmark value): 8q/2kv heads of the 32k prefill, decode batch 16',
+                      l2='inputs larger than L2 (q+k+v+o = 168 MB per step)')
 
     if args.impl == 'reference':
         if rank != 0:
