@@ -75,6 +75,26 @@ int nats_b200_prefill_fwd(const void* d_q, const void* d_k, const void* d_v, voi
                           void* d_workspace, size_t workspace_bytes, int64_t* d_kept_tiles, int32_t* d_status,
                           void* stream);
 
+/* Same computation as nats_b200_prefill_fwd for callers that have no way to hand over a workspace: code running
+ * where device allocation is off limits -- inside a latency-critical serving loop that must not touch the allocator,
+ * in a process whose memory pool is owned and fully handed out by another framework, or in a plugin host that gives
+ * a kernel library nothing but its input and output buffers.  (No counterpart in the reference: its Triton entry
+ * points allocate freely through PyTorch.)
+ * The role metadata goes to a scratch array built into the library: nats_b200_prefill_static_scratch_bytes() bytes
+ * (1 MiB) of device memory per GPU that loads the library, held until the process exits.  Shapes whose metadata
+ * does not fit -- B*Hkv*(ceil(N/C) + 2*ceil(N/128)) int32 values plus padding -- are rejected with NATS_ERR_WORKSPACE.
+ * This call and the library allocate nothing: no cudaMalloc / cudaFree, no allocating library routine.
+ * The first call on a device looks up the scratch array's device address (once per device, with that device
+ * current); make that first call before any stream capture begins.
+ * Every call on a device shares the one array and overwrites all of the metadata it reads, so nothing carries over
+ * from the previous call; but two calls that overlap on the GPU (different streams, no ordering between them) race
+ * on it -- keep calls on one device ordered.
+ */
+size_t nats_b200_prefill_static_scratch_bytes(void);
+int nats_b200_prefill_fwd_static(const void* d_q, const void* d_k, const void* d_v, void* d_o, const uint8_t* d_roles,
+                                 int B, int Hq, int Hkv, int N, int D, int C, int SW, float sm_scale,
+                                 int64_t* d_kept_tiles, int32_t* d_status, void* stream);
+
 /* ------------------------------------------------------------------------------------------------
  * Eviction after the first prefill call, in two steps because the size of the compacted cache is data dependent.
  *

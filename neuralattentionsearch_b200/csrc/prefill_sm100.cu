@@ -618,3 +618,54 @@ extern "C" __attribute__((visibility("default"))) int nats_b200_prefill_fwd(cons
     if (D == 64) return launch_prefill<64>(mq, mk, mv, p, B, (cudaStream_t)stream);
     return launch_prefill<128>(mq, mk, mv, p, B, (cudaStream_t)stream);
 }
+
+// =================================================================================================
+// Prefill without any allocation by the caller or by this library
+// =================================================================================================
+namespace nats {
+
+constexpr size_t kStaticScratchBytes = 1u << 20;   // 1 MiB per GPU that loads the library, held until the process exits
+constexpr int kMaxDevices = 64;
+
+// Scratch for the role metadata (row limits and per-tile max / min limits) of nats_b200_prefill_fwd_static.
+// In host code this name is only a stand-in for the symbol: the device address is obtained once per device below.
+static __device__ __align__(256) uint8_t g_prefill_scratch[kStaticScratchBytes];
+static void* g_prefill_scratch_addr[kMaxDevices] = {};
+
+// Device address of the scratch array on the current device; looked up on the first call per device.
+static int static_scratch(void** out) {
+    int dev = -1;
+    NATS_CHECK_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= kMaxDevices) return fail(NATS_ERR_UNSUPPORTED, "device index %d is outside [0, %d)", dev, kMaxDevices);
+    if (g_prefill_scratch_addr[dev] == nullptr) {
+        void* ptr = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&ptr, g_prefill_scratch);
+        if (e != cudaSuccess || ptr == nullptr)
+            return fail(NATS_ERR_CUDA, "cudaGetSymbolAddress(g_prefill_scratch) failed on device %d: %s", dev, cudaGetErrorString(e));
+        g_prefill_scratch_addr[dev] = ptr;
+    }
+    *out = g_prefill_scratch_addr[dev];
+    return NATS_OK;
+}
+
+}  // namespace nats
+
+extern "C" __attribute__((visibility("default"))) size_t nats_b200_prefill_static_scratch_bytes(void) {
+    return nats::kStaticScratchBytes;
+}
+
+extern "C" __attribute__((visibility("default"))) int nats_b200_prefill_fwd_static(
+    const void* d_q, const void* d_k, const void* d_v, void* d_o, const uint8_t* d_roles,
+    int B, int Hq, int Hkv, int N, int D, int C, int SW, float sm_scale,
+    int64_t* d_kept_tiles, int32_t* d_status, void* stream) {
+    if (B <= 0 || Hkv <= 0 || N <= 0 || C <= 0) return fail(NATS_ERR_INVALID_ARG, "bad shape B=%d Hkv=%d N=%d C=%d", B, Hkv, N, C);
+    const size_t need = nats_b200_prefill_workspace_bytes(B, Hkv, N, C);
+    if (need > nats::kStaticScratchBytes)
+        return fail(NATS_ERR_WORKSPACE,
+                    "this shape needs %zu bytes of role metadata, the built-in scratch holds %zu: use nats_b200_prefill_fwd "
+                    "with a caller-provided workspace", need, (size_t)nats::kStaticScratchBytes);
+    void* scratch = nullptr;
+    if (int rc = nats::static_scratch(&scratch)) return rc;
+    return nats_b200_prefill_fwd(d_q, d_k, d_v, d_o, d_roles, B, Hq, Hkv, N, D, C, SW, sm_scale, scratch,
+                                 nats::kStaticScratchBytes, d_kept_tiles, d_status, stream);
+}
