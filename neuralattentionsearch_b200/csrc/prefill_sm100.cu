@@ -39,6 +39,18 @@ struct PrefillParams {
     float scale_log2;
 };
 
+#ifdef NATS_TRACE
+// Development aid (never compiled into the shipped library): cycle stamps of the first CTA's pipeline stages.
+__device__ long long g_trace[2 * 64 * 8];
+#define NATS_STAMP(role, jt, slot)                                                                      \
+    do {                                                                                                \
+        if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0 && (jt) < 64)           \
+            g_trace[((role) * 64 + (jt)) * 8 + (slot)] = clock64();                                     \
+    } while (0)
+#else
+#define NATS_STAMP(role, jt, slot) do {} while (0)
+#endif
+
 // ---- PTX wrappers -------------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -110,12 +122,13 @@ __device__ __forceinline__ void tc_commit(uint32_t bar) {
 __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
-// D[tmem] (+)= A[smem desc] * B[smem desc]
-__device__ __forceinline__ void mma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+// D[tmem] (+)= A[smem desc] * B[smem desc]; ACC is a compile-time flag so that no predicate has to be computed per MMA
+template <int ACC>
+__device__ __forceinline__ void mma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc) {
     asm volatile(
         "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "n"(ACC) : "memory");
 }
 // D[tmem] (+)= A[tmem] * B[smem desc]
 __device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
@@ -157,6 +170,14 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16
           "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
           "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
         : "memory");
+}
+
+// bits [lo, hi) of a 128-bit row mask that fall into its 32-bit word w
+__device__ __forceinline__ uint32_t range_mask(int lo, int hi, int w) {
+    const int a = max(lo - 32 * w, 0), b = min(hi - 32 * w, 32);
+    if (b <= a) return 0u;
+    const uint32_t upto_b = (b >= 32) ? 0xffffffffu : ((1u << b) - 1u);
+    return upto_b & ~((1u << a) - 1u);
 }
 
 __device__ __forceinline__ float ex2(float x) {
@@ -219,6 +240,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     const int q_hi = min(q_lo + kTile, p.N) - 1;
     volatile int* abort_flag = &sm.abort_flag;
 
+    if (warp == 1) NATS_STAMP(1, 60, 7);
     if (tid == 0) sm.abort_flag = (*reinterpret_cast<volatile int32_t*>(p.status) != 0);
     __syncthreads();
     if (sm.abort_flag) return;                         // an earlier CTA gave up: do not start (uniform for the CTA)
@@ -292,9 +314,13 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         __syncthreads();
     }
     const int n_kept = sm.n_kept;
+    if (warp == 1) NATS_STAMP(1, 61, 7);
     tc_fence_after();
     const uint32_t tmem = sm.tmem_base;
 
+    // Register budget: the softmax warpgroups hold a whole score row per thread (setmaxnreg.inc at the top of their
+    // branch), the producer / issuer warpgroup needs little and gives registers back (setmaxnreg.dec in its branches).
+    if (warp < 4) asm volatile("setmaxnreg.dec.sync.aligned.u32 48;");      // one site for the whole warpgroup
     if (warp == 0) {
         // =============================== TMA producer ===============================
         int issued_k = 0, issued_v = 0;
@@ -331,22 +357,29 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     } else if (warp == 1) {
         // =============================== MMA issuer ===============================
         bool ok = mbar_wait(smem_u32(&sm.bar_q), 0, abort_flag, p.status, kErrQ);
+        // descriptors of the tiles: only the start-address field (low word, in 16-byte units) moves between MMAs
+        const uint64_t q_desc0 = smem_desc(smem_u32(&sm.q[0][0]), 16, 1024);
+        const uint64_t k_desc0 = smem_desc(smem_u32(&sm.k[0][0]), 16, 1024);
+        const uint64_t v_desc0 = smem_desc(smem_u32(&sm.v[0][0]), kBoxBytes, 1024);
+        constexpr uint32_t TILE16 = TILE_BYTES >> 4;
         auto issue_qk = [&](int h, int s) {
             // S_h[128 x 128] = Q_h[128 x D] . K[128 x D]^T : D/16 MMAs of K = 16
-            const uint32_t qa = smem_u32(&sm.q[h][0]), ka = smem_u32(&sm.k[s][0]);
+            const uint64_t qd = q_desc0 + (uint64_t)(h * TILE16), kd = k_desc0 + (uint64_t)(s * TILE16);
+            const uint32_t dS = tmem + h * 128;
+            mma_ss<0>(dS, qd, kd, IDESC_QK);
 #pragma unroll
-            for (int ks = 0; ks < D / 16; ++ks) {
-                const uint32_t off = (ks / 4) * kBoxBytes + (ks % 4) * 32;
-                mma_ss(tmem + h * 128, smem_desc(qa + off, 16, 1024), smem_desc(ka + off, 16, 1024), IDESC_QK, ks > 0);
+            for (int ks = 1; ks < D / 16; ++ks) {
+                const uint32_t off16 = ((ks / 4) * kBoxBytes + (ks % 4) * 32) >> 4;
+                mma_ss<1>(dS, qd + off16, kd + off16, IDESC_QK);
             }
         };
         auto issue_pv = [&](int h, int s, bool first) {
             // O_h[128 x D] (+)= P_h[128 x 128] . V[128 x D] : 8 MMAs of K = 16; V is MN-major (D contiguous)
-            const uint32_t va = smem_u32(&sm.v[s][0]);
+            const uint64_t vd = v_desc0 + (uint64_t)(s * TILE16);
+            const uint32_t dO = tmem + 256 + h * 128, aP = tmem + h * 128;
+            mma_ts(dO, aP, vd, IDESC_PV, first ? 0u : 1u);
 #pragma unroll
-            for (int ks = 0; ks < 8; ++ks)
-                mma_ts(tmem + 256 + h * 128, tmem + h * 128 + ks * 8, smem_desc(va + ks * 2048, kBoxBytes, 1024), IDESC_PV,
-                       (first && ks == 0) ? 0u : 1u);
+            for (int ks = 1; ks < 8; ++ks) mma_ts(dO, aP + ks * 8, vd + (uint64_t)(ks * (2048 >> 4)), IDESC_PV, 1u);
         };
         if (ok && n_kept > 0) {
             ok = mbar_wait(smem_u32(&sm.bar_k_full[0]), 0, abort_flag, p.status, kErrKFull);
@@ -368,11 +401,16 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             const bool has_next = jt + 1 < n_kept;
             const int sn = (jt + 1) % kStages;
             const uint32_t phn = ((jt + 1) / kStages) & 1;
+            NATS_STAMP(1, jt, 3);
             ok = mbar_wait(smem_u32(&sm.bar_v_full[s]), ph, abort_flag, p.status, kErrVFull);
+            NATS_STAMP(1, jt, 7);
             for (int h = 0; h < nslots && ok; ++h) {
+                NATS_STAMP(1, jt, h * 4 + 0);
                 ok = mbar_wait(smem_u32(&sm.bar_p_full[h]), jt & 1, abort_flag, p.status, kErrPFull);
+                NATS_STAMP(1, jt, h * 4 + 1);
                 if (ok && has_next && h == 0) ok = mbar_wait(smem_u32(&sm.bar_k_full[sn]), phn, abort_flag, p.status, kErrKFull);
                 if (!ok) break;
+                NATS_STAMP(1, jt, h * 4 + 1);
                 tc_fence_after();
                 if (lane == 0) {
                     issue_pv(h, s, jt == 0);
@@ -384,11 +422,13 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                         if (h == nslots - 1) tc_commit(smem_u32(&sm.bar_k_empty[sn]));
                     }
                 }
+                NATS_STAMP(1, jt, h * 4 + 2);
                 __syncwarp();
             }
         }
     } else if (warp >= 4 && warp < 4 + 4 * nslots) {
         // =============================== softmax + epilogue ===============================
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
         const int h = (warp - 4) / 4;                    // head slot
         const int row = (warp & 3) * 32 + lane;          // query row inside the tile == TMEM lane
         const int qi = q_lo + row;                       // query token index
@@ -403,29 +443,51 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             const int entry = sm.list[jt];
             const int kt = entry & 0x7fff;
             const bool partial = (entry & 0x8000) != 0;
+            // visibility bits of this row for the 128 columns of a tile that is not fully visible
+            uint32_t bits[4] = {0xffffffffu, 0xffffffffu, 0xffffffffu, 0xffffffffu};
+            if (partial) {
+                // columns this row may see: the causal prefix (and nothing past N), minus every chunk whose row limit is below it
+                const int k0 = kt * kTile;
+                const int nvis = max(0, min(min(qi - k0 + 1, p.N - k0), kTile));
+#pragma unroll
+                for (int w = 0; w < 4; ++w) bits[w] = range_mask(0, nvis, w);
+                const int c_first = k0 / p.C, c_last = min((k0 + kTile - 1) / p.C, p.Nc - 1);
+#pragma unroll 1
+                for (int cc = c_first; cc <= c_last; ++cc) {
+                    if (qi > lim[cc]) {
+                        const int lo = max(cc * p.C - k0, 0), hi = min((cc + 1) * p.C - k0, kTile);
+#pragma unroll
+                        for (int w = 0; w < 4; ++w) bits[w] &= ~range_mask(lo, hi, w);
+                    }
+                }
+            }
+            if (warp == 4) NATS_STAMP(0, jt, 0);
             ok = mbar_wait(smem_u32(&sm.bar_s_full[h]), jt & 1, abort_flag, p.status, kErrSFull);
             if (!ok) break;
             tc_fence_after();
-            // pass 1: row maximum of the visible scores
-            float mx = -INFINITY;
-#pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
-                uint32_t r[32];
-                tmem_ld32(tS + c * 32, r);
-                tc_wait_ld();
-                if (partial) {
+            if (warp == 4) NATS_STAMP(0, jt, 1);
+            // the whole score row of this thread in registers: four loads in flight, one wait
+            uint32_t sreg[128];
+            tmem_ld32(tS + 0, *reinterpret_cast<uint32_t(*)[32]>(&sreg[0]));
+            tmem_ld32(tS + 32, *reinterpret_cast<uint32_t(*)[32]>(&sreg[32]));
+            tmem_ld32(tS + 64, *reinterpret_cast<uint32_t(*)[32]>(&sreg[64]));
+            tmem_ld32(tS + 96, *reinterpret_cast<uint32_t(*)[32]>(&sreg[96]));
+            tc_wait_ld();
+            if (partial) {
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        const int kj = kt * kTile + c * 32 + i;
-                        const bool vis = kj <= qi && (kj < p.N) && qi <= lim[kj / p.C];
-                        if (vis) mx = fmaxf(mx, __uint_as_float(r[i]));
-                    }
-                } else {
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
-                }
+                for (int i = 0; i < 128; ++i)
+                    if (!((bits[i >> 5] >> (i & 31)) & 1u)) sreg[i] = 0xff800000u;      // -inf: exp2 gives exactly 0
             }
-            mx *= scale;                                    // scale > 0
+            float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+            for (int i = 0; i < 128; i += 4) {
+                mx0 = fmaxf(mx0, __uint_as_float(sreg[i]));
+                mx1 = fmaxf(mx1, __uint_as_float(sreg[i + 1]));
+                mx2 = fmaxf(mx2, __uint_as_float(sreg[i + 2]));
+                mx3 = fmaxf(mx3, __uint_as_float(sreg[i + 3]));
+            }
+            const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * scale;       // scale > 0
+            if (warp == 4) NATS_STAMP(0, jt, 2);
             // online softmax with lazy rescaling: the reference maximum only moves when the row max grew by > threshold
             float alpha = 1.f;
             bool need = false;
@@ -449,35 +511,29 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                     tmem_st32(tO + c * 32, r);
                 }
             }
-            const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
-            // pass 2: P = exp2(S * scale - m), row sum in fp32, P packed to bf16 over the first 64 columns of S_h
-#pragma unroll 1
+            const float m_neg = (m_ref == -INFINITY) ? 0.f : -m_ref;
+            if (warp == 4) NATS_STAMP(0, jt, 3);
+            // P = exp2(S * scale - m), row sum in fp32, P packed to bf16 over the first 64 columns of S_h
+            float ls0 = 0.f, ls1 = 0.f;
+#pragma unroll
             for (int c = 0; c < 4; ++c) {
-                uint32_t r[32];
-                tmem_ld32(tS + c * 32, r);
-                tc_wait_ld();
                 uint32_t pk[16];
-                float ls = 0.f;
 #pragma unroll
                 for (int i = 0; i < 32; i += 2) {
-                    float p0 = ex2(fmaf(__uint_as_float(r[i]), scale, -m_use));
-                    float p1 = ex2(fmaf(__uint_as_float(r[i + 1]), scale, -m_use));
-                    if (partial) {
-                        const int kj = kt * kTile + c * 32 + i;
-                        const bool v0 = kj <= qi && (kj < p.N) && qi <= lim[kj / p.C];
-                        const bool v1 = (kj + 1) <= qi && (kj + 1 < p.N) && qi <= lim[(kj + 1) / p.C];
-                        p0 = v0 ? p0 : 0.f;
-                        p1 = v1 ? p1 : 0.f;
-                    }
-                    ls += p0 + p1;
+                    const float p0 = ex2(fmaf(__uint_as_float(sreg[c * 32 + i]), scale, m_neg));
+                    const float p1 = ex2(fmaf(__uint_as_float(sreg[c * 32 + i + 1]), scale, m_neg));
+                    ls0 += p0;
+                    ls1 += p1;
                     pk[i / 2] = pack_bf16(p0, p1);
                 }
-                l_sum += ls;
                 tmem_st16(tS + c * 16, pk);
             }
+            l_sum += ls0 + ls1;
+            if (warp == 4) NATS_STAMP(0, jt, 4);
             tc_wait_st();
             tc_fence_before();
             mbar_arrive(smem_u32(&sm.bar_p_full[h]));
+            if (warp == 4) NATS_STAMP(0, jt, 5);
         }
         // epilogue: O / l -> bf16 -> global
         if (ok && n_kept > 0) ok = mbar_wait(smem_u32(&sm.bar_o_full[h]), 0, abort_flag, p.status, kErrOFull);
@@ -505,8 +561,10 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         }
     }
     // ---- teardown ----
+    if (warp == 1) NATS_STAMP(1, 62, 7);
     tc_fence_before();
     __syncthreads();
+    if (warp == 1) NATS_STAMP(1, 63, 7);
     if (warp == 1) {
         if (sm.abort_flag) {
             // MMAs may still be running: give them time before the accumulator columns are released
@@ -669,3 +727,9 @@ extern "C" __attribute__((visibility("default"))) int nats_b200_prefill_fwd_stat
     return nats_b200_prefill_fwd(d_q, d_k, d_v, d_o, d_roles, B, Hq, Hkv, N, D, C, SW, sm_scale, scratch,
                                  nats::kStaticScratchBytes, d_kept_tiles, d_status, stream);
 }
+
+#ifdef NATS_TRACE
+extern "C" __attribute__((visibility("default"))) int nats_b200_debug_trace(long long* host_out) {
+    return (int)cudaMemcpyFromSymbol(host_out, nats::g_trace, sizeof(long long) * 2 * 64 * 8);
+}
+#endif
