@@ -5,7 +5,7 @@
 // work on S = Q.K^T in TMEM, the tensor core runs the other head's MMAs.
 //
 //   warp 0      TMA producer: Q (once), then K and V of every kept KV tile through 2-stage rings
-//   warp 1      MMA issuer (one elected lane): S_h = Q_h.K^T (SS), O_h += P_h.V (TS, P read from TMEM)
+//   warps 1,2   MMA issuers of head slot 0 / 1 (one elected lane each): S_h = Q_h.K^T (SS), O_h += P_h.V (TS, P from TMEM)
 //   warps 4-7   softmax of head slot 0: one thread per query row, S read with tcgen05.ld, online softmax in
 //   warps 8-11  softmax of head slot 1  registers, P written back over S as packed bf16 with tcgen05.st
 //
@@ -27,7 +27,7 @@ constexpr uint32_t kBoxBytes = 128 * 64 * 2;            // one TMA box: 128 rows
 constexpr float kRescaleThreshold = 8.0f;               // log2 units: O is rescaled only when the row max grows by more
 constexpr unsigned long long kWaitLimitNs = 400ull * 1000ull * 1000ull;
 
-enum : int { kErrQ = 1, kErrKFull, kErrVFull, kErrKEmpty, kErrVEmpty, kErrSFull, kErrPFull, kErrOFull };
+enum : int { kErrQ = 1, kErrKFull, kErrVFull, kErrKEmpty, kErrVEmpty, kErrSFull, kErrPFull, kErrOFull, kErrTurn };
 
 struct PrefillParams {
     __nv_bfloat16* o;                 // [B,Hq,N,D]
@@ -213,7 +213,7 @@ struct __align__(1024) PrefillSmem {
     uint16_t list[kMaxTiles];              // kept KV tiles of this query tile, ascending; bit 15 = needs element masking
     int seg_count[kMaxTiles / 32];
     unsigned long long bar_q, bar_k_full[kStages], bar_k_empty[kStages], bar_v_full[kStages], bar_v_empty[kStages];
-    unsigned long long bar_s_full[2], bar_p_full[2], bar_o_full[2];
+    unsigned long long bar_s_full[2], bar_p_full[2], bar_o_full[2], bar_turn[2];
     uint32_t tmem_base;
     int n_kept;
     int abort_flag;
@@ -250,14 +250,15 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         mbar_init(smem_u32(&sm.bar_q), 1);
         for (int s = 0; s < kStages; ++s) {
             mbar_init(smem_u32(&sm.bar_k_full[s]), 1);
-            mbar_init(smem_u32(&sm.bar_k_empty[s]), 1);
+            mbar_init(smem_u32(&sm.bar_k_empty[s]), nslots);      // one commit per MMA issuer
             mbar_init(smem_u32(&sm.bar_v_full[s]), 1);
-            mbar_init(smem_u32(&sm.bar_v_empty[s]), 1);
+            mbar_init(smem_u32(&sm.bar_v_empty[s]), nslots);
         }
         for (int h = 0; h < 2; ++h) {
             mbar_init(smem_u32(&sm.bar_s_full[h]), 1);
             mbar_init(smem_u32(&sm.bar_p_full[h]), 128);
             mbar_init(smem_u32(&sm.bar_o_full[h]), 1);
+            mbar_init(smem_u32(&sm.bar_turn[h]), 1);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         prefetch_tmap(&map_q);
@@ -354,43 +355,49 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             for (int jt = max(0, issued_v - kStages); jt < issued_v; ++jt)
                 mbar_wait(smem_u32(&sm.bar_v_full[jt % kStages]), (jt / kStages) & 1, nullptr, p.status, kErrVFull);
         }
-    } else if (warp == 1) {
-        // =============================== MMA issuer ===============================
+    } else if (warp == 1 || (warp == 2 && nslots == 2)) {
+        // =============================== MMA issuers: warp 1 for head slot 0, warp 2 for head slot 1 ===============================
+        // Each issuer owns the chain of its head: O_h += P_h.V for tile j, then S_h = Q_h.K^T for tile j+1 (which may only
+        // overwrite S_h once the MMA reading P_h from it has been issued).  While one issuer waits for its softmax
+        // warps, the tensor core runs the other issuer's MMAs.  K/V stages are released when both issuers have committed.
+        const int h = warp - 1;
+        const bool two = nslots == 2;
         bool ok = mbar_wait(smem_u32(&sm.bar_q), 0, abort_flag, p.status, kErrQ);
         // descriptors of the tiles: only the start-address field (low word, in 16-byte units) moves between MMAs
-        const uint64_t q_desc0 = smem_desc(smem_u32(&sm.q[0][0]), 16, 1024);
+        constexpr uint32_t TILE16 = TILE_BYTES >> 4;
+        const uint64_t q_desc = smem_desc(smem_u32(&sm.q[0][0]), 16, 1024) + (uint64_t)(h * TILE16);
         const uint64_t k_desc0 = smem_desc(smem_u32(&sm.k[0][0]), 16, 1024);
         const uint64_t v_desc0 = smem_desc(smem_u32(&sm.v[0][0]), kBoxBytes, 1024);
-        constexpr uint32_t TILE16 = TILE_BYTES >> 4;
-        auto issue_qk = [&](int h, int s) {
+        const uint32_t dS = tmem + h * 128, dO = tmem + 256 + h * 128;
+        auto issue_qk = [&](int s) {
             // S_h[128 x 128] = Q_h[128 x D] . K[128 x D]^T : D/16 MMAs of K = 16
-            const uint64_t qd = q_desc0 + (uint64_t)(h * TILE16), kd = k_desc0 + (uint64_t)(s * TILE16);
-            const uint32_t dS = tmem + h * 128;
-            mma_ss<0>(dS, qd, kd, IDESC_QK);
+            const uint64_t kd = k_desc0 + (uint64_t)(s * TILE16);
+            mma_ss<0>(dS, q_desc, kd, IDESC_QK);
 #pragma unroll
             for (int ks = 1; ks < D / 16; ++ks) {
                 const uint32_t off16 = ((ks / 4) * kBoxBytes + (ks % 4) * 32) >> 4;
-                mma_ss<1>(dS, qd + off16, kd + off16, IDESC_QK);
+                mma_ss<1>(dS, q_desc + off16, kd + off16, IDESC_QK);
             }
         };
-        auto issue_pv = [&](int h, int s, bool first) {
+        auto issue_pv = [&](int s, bool first) {
             // O_h[128 x D] (+)= P_h[128 x 128] . V[128 x D] : 8 MMAs of K = 16; V is MN-major (D contiguous)
             const uint64_t vd = v_desc0 + (uint64_t)(s * TILE16);
-            const uint32_t dO = tmem + 256 + h * 128, aP = tmem + h * 128;
-            mma_ts(dO, aP, vd, IDESC_PV, first ? 0u : 1u);
+            mma_ts(dO, dS, vd, IDESC_PV, first ? 0u : 1u);
 #pragma unroll
-            for (int ks = 1; ks < 8; ++ks) mma_ts(dO, aP + ks * 8, vd + (uint64_t)(ks * (2048 >> 4)), IDESC_PV, 1u);
+            for (int ks = 1; ks < 8; ++ks) mma_ts(dO, dS + ks * 8, vd + (uint64_t)(ks * (2048 >> 4)), IDESC_PV, 1u);
         };
         if (ok && n_kept > 0) {
             ok = mbar_wait(smem_u32(&sm.bar_k_full[0]), 0, abort_flag, p.status, kErrKFull);
+            // The two issuers take turns (a token passed through bar_turn): the heads stay half a period apart, so one
+            // head's exponentials overlap the other head's MMAs instead of both competing for the same unit at once.
+            if (ok && two && h == 1) ok = mbar_wait(smem_u32(&sm.bar_turn[1]), 0, abort_flag, p.status, kErrTurn);
             if (ok) {
                 tc_fence_after();
                 if (lane == 0) {
-                    for (int h = 0; h < nslots; ++h) {
-                        issue_qk(h, 0);
-                        tc_commit(smem_u32(&sm.bar_s_full[h]));
-                    }
+                    issue_qk(0);
+                    tc_commit(smem_u32(&sm.bar_s_full[h]));
                     tc_commit(smem_u32(&sm.bar_k_empty[0]));
+                    if (two) mbar_arrive(smem_u32(&sm.bar_turn[1 - h]));
                 }
                 __syncwarp();
             }
@@ -401,30 +408,28 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             const bool has_next = jt + 1 < n_kept;
             const int sn = (jt + 1) % kStages;
             const uint32_t phn = ((jt + 1) / kStages) & 1;
-            NATS_STAMP(1, jt, 3);
+            if (warp == 1) NATS_STAMP(1, jt, 0);
             ok = mbar_wait(smem_u32(&sm.bar_v_full[s]), ph, abort_flag, p.status, kErrVFull);
-            NATS_STAMP(1, jt, 7);
-            for (int h = 0; h < nslots && ok; ++h) {
-                NATS_STAMP(1, jt, h * 4 + 0);
-                ok = mbar_wait(smem_u32(&sm.bar_p_full[h]), jt & 1, abort_flag, p.status, kErrPFull);
-                NATS_STAMP(1, jt, h * 4 + 1);
-                if (ok && has_next && h == 0) ok = mbar_wait(smem_u32(&sm.bar_k_full[sn]), phn, abort_flag, p.status, kErrKFull);
-                if (!ok) break;
-                NATS_STAMP(1, jt, h * 4 + 1);
-                tc_fence_after();
-                if (lane == 0) {
-                    issue_pv(h, s, jt == 0);
-                    if (!has_next) tc_commit(smem_u32(&sm.bar_o_full[h]));
-                    if (h == nslots - 1) tc_commit(smem_u32(&sm.bar_v_empty[s]));
-                    if (has_next) {
-                        issue_qk(h, sn);
-                        tc_commit(smem_u32(&sm.bar_s_full[h]));
-                        if (h == nslots - 1) tc_commit(smem_u32(&sm.bar_k_empty[sn]));
-                    }
+            if (ok && has_next) ok = mbar_wait(smem_u32(&sm.bar_k_full[sn]), phn, abort_flag, p.status, kErrKFull);
+            if (ok) ok = mbar_wait(smem_u32(&sm.bar_p_full[h]), jt & 1, abort_flag, p.status, kErrPFull);
+            // turn n = jt + 1 of this issuer: issuer 0 follows issuer 1's turn n - 1, issuer 1 follows issuer 0's turn n
+            if (ok && two) ok = mbar_wait(smem_u32(&sm.bar_turn[h]), (h == 0 ? jt : jt + 1) & 1, abort_flag, p.status, kErrTurn);
+            if (!ok) break;
+            if (warp == 1) NATS_STAMP(1, jt, 1);
+            tc_fence_after();
+            if (lane == 0) {
+                issue_pv(s, jt == 0);
+                if (!has_next) tc_commit(smem_u32(&sm.bar_o_full[h]));
+                tc_commit(smem_u32(&sm.bar_v_empty[s]));
+                if (has_next) {
+                    issue_qk(sn);
+                    tc_commit(smem_u32(&sm.bar_s_full[h]));
+                    tc_commit(smem_u32(&sm.bar_k_empty[sn]));
                 }
-                NATS_STAMP(1, jt, h * 4 + 2);
-                __syncwarp();
+                if (two) mbar_arrive(smem_u32(&sm.bar_turn[1 - h]));
             }
+            if (warp == 1) NATS_STAMP(1, jt, 2);
+            __syncwarp();
         }
     } else if (warp >= 4 && warp < 4 + 4 * nslots) {
         // =============================== softmax + epilogue ===============================
