@@ -300,8 +300,16 @@ __global__ void __launch_bounds__(kCopyThreads) decode_place_kernel(const PlaceP
     }
     __syncthreads();   // every read of the pending chunk is done before the region behind the new length is cleared
     if (trow < tpp) {
+        // cleared: the locals a global chunk has just dropped, [new_len, len), and the slot of the pending chunk unless the
+        // chunk stayed there; everything else behind a head's length is zero already
+        for (int d = new_len + trow; d < len; d += tpp) {
+            const size_t o = (size_t)d * p.rowB + tvec;
+            st16(ck + o, zero);
+            st16(cv + o, zero);
+            if (tvec == 0) valid[d] = 0;
+        }
         const int end = min(T0 + p.C, p.Lcap);
-        for (int d = new_len + trow; d < end; d += tpp) {
+        for (int d = max(T0, new_len) + trow; d < end; d += tpp) {
             const size_t o = (size_t)d * p.rowB + tvec;
             st16(ck + o, zero);
             st16(cv + o, zero);

@@ -14,6 +14,7 @@ namespace nats {
 constexpr int kSeg = 512;          // logical tokens per block
 constexpr int kDecThreads = 128;
 constexpr int kDecWarps = kDecThreads / 32;
+constexpr int kDecStages = 3;       // ring depth per warp: two iterations of loads in flight while one is consumed
 
 struct DecodeParams {
     const __nv_bfloat16* q;        // [B,Hq,1,D]
@@ -45,6 +46,16 @@ __device__ __forceinline__ float fast_exp2(float x) {
     return y;
 }
 
+// 16-byte asynchronous global -> shared copy that bypasses L1; with valid == false nothing is read and zeros are written
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc, bool valid) {
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
+    const int n = valid ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(gsrc), "r"(n) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
 template <int D, int NREP, int U>
 __global__ void __launch_bounds__(kDecThreads) decode_kernel(const DecodeParams p) {
     constexpr int TPR = D / 8;                       // lanes per row
@@ -68,9 +79,20 @@ __global__ void __launch_bounds__(kDecThreads) decode_kernel(const DecodeParams 
     if (seg >= nsplit) return;
     const int r0 = seg * kSeg, r1 = min(Ltot, r0 + kSeg);
 
+    // Dynamic shared memory: per warp a ring of kDecStages stages; a stage holds, for each of the U passes, the 16 bytes of
+    // K and of V every lane has asked for (cp.async), so the bytes in flight do not occupy registers.  Each lane only ever
+    // reads back what it copied itself, so cp.async.wait_group is the only synchronisation.  After the main loop the
+    // same memory holds the per-lane-group partial results that are combined across the block.
+    extern __shared__ __align__(16) uint8_t dsm[];
+    constexpr int STAGE_BYTES = U * 2 * 32 * 16;
+    constexpr int RING_BYTES = kDecWarps * kDecStages * STAGE_BYTES;
+    constexpr int COMBINE_BYTES = G * NREP * (D + 2) * 4;
+    static_assert(COMBINE_BYTES <= RING_BYTES, "combine scratch must fit into the ring");
+    uint8_t* ring = dsm + warp * kDecStages * STAGE_BYTES + lane * 16;
+    float (*s_acc)[NREP][D] = reinterpret_cast<float (*)[NREP][D]>(dsm);
+    float (*s_m)[NREP] = reinterpret_cast<float (*)[NREP]>(dsm + G * NREP * D * 4);
+    float (*s_l)[NREP] = reinterpret_cast<float (*)[NREP]>(dsm + G * NREP * (D + 1) * 4);
     __shared__ uint8_t s_ring_ok[kSeg];
-    __shared__ float s_m[G][NREP], s_l[G][NREP];
-    __shared__ __align__(16) float s_acc[G][NREP][D];
     __shared__ int s_last;
 
     const size_t row_elems = (size_t)D;
@@ -110,11 +132,10 @@ __global__ void __launch_bounds__(kDecThreads) decode_kernel(const DecodeParams 
 #pragma unroll
     for (int r = 0; r < R; ++r) { m_own[r] = NEG_INF; l_own[r] = 0.f; }
 
-    const uint4 zero4 = make_uint4(0, 0, 0, 0);
-    for (int base = r0; base < r1; base += ROWS_IT) {
-        uint4 kq[U], vq[U];
-        unsigned okmask = 0;
-        const __nv_bfloat16* vp[U];
+    // issue the copies of iteration `it` into its ring stage (rows that do not exist or are invalid are zero-filled)
+    auto issue = [&](int it) {
+        const int base = r0 + it * ROWS_IT;
+        uint8_t* dst = ring + (it % kDecStages) * STAGE_BYTES;
 #pragma unroll
         for (int u = 0; u < U; ++u) {
             const int i = base + u * (kDecWarps * RPW) + warp * RPW + grp;
@@ -126,12 +147,32 @@ __global__ void __launch_bounds__(kDecThreads) decode_kernel(const DecodeParams 
                 else if (i < len + p.fill) { const size_t ph = (size_t)(T0 + (i - len)); kp = ck + ph * row_elems; vpp = cv + ph * row_elems; }
                 else { kp = kn; vpp = vn; }
             }
-            kq[u] = ok ? ld16_stream(kp + j * 8) : zero4;
-            vp[u] = vpp;
-            okmask |= (ok ? 1u : 0u) << u;
+            cp_async16(dst + (u * 2 + 0) * 512, kp + j * 8, ok);
+            cp_async16(dst + (u * 2 + 1) * 512, vpp + j * 8, ok);
         }
+    };
+    const int n_it = (r1 - r0 + ROWS_IT - 1) / ROWS_IT;
 #pragma unroll
-        for (int u = 0; u < U; ++u) vq[u] = ((okmask >> u) & 1u) ? ld16_stream(vp[u] + j * 8) : zero4;
+    for (int it = 0; it < kDecStages - 1; ++it) {
+        if (it < n_it) issue(it);
+        cp_async_commit();
+    }
+    for (int it = 0; it < n_it; ++it) {
+        if (it + kDecStages - 1 < n_it) issue(it + kDecStages - 1);
+        cp_async_commit();
+        cp_async_wait<kDecStages - 1>();
+        const int base = r0 + it * ROWS_IT;
+        const uint8_t* src = ring + (it % kDecStages) * STAGE_BYTES;
+        uint4 kq[U], vq[U];
+        unsigned okmask = 0;
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int i = base + u * (kDecWarps * RPW) + warp * RPW + grp;
+            const bool ok = i < r1 && (i >= p.SW || s_ring_ok[i - r0] != 0);
+            okmask |= (ok ? 1u : 0u) << u;
+            kq[u] = *reinterpret_cast<const uint4*>(src + (u * 2 + 0) * 512);
+            vq[u] = *reinterpret_cast<const uint4*>(src + (u * 2 + 1) * 512);
+        }
 
         float part[V];
 #pragma unroll
@@ -226,7 +267,9 @@ __global__ void __launch_bounds__(kDecThreads) decode_kernel(const DecodeParams 
         }
     }
 
-    // ---- combine the lane groups of this block ----
+    // ---- combine the lane groups of this block (the ring is drained: every copy was waited for) ----
+    cp_async_wait<0>();
+    __syncthreads();
     const int g = warp * RPW + grp;
     if constexpr (FAST) {
 #pragma unroll
@@ -306,7 +349,14 @@ template <int D, int NREP>
 static cudaError_t launch_decode(const DecodeParams& p, dim3 grid, cudaStream_t st) {
     constexpr int TPR = D / 8;
     constexpr int U = (NREP * 4 >= TPR) ? 4 : ((NREP * 8 >= TPR) ? 8 : 4);
-    decode_kernel<D, NREP, U><<<grid, kDecThreads, 0, st>>>(p);
+    constexpr int smem = kDecWarps * kDecStages * U * 2 * 32 * 16;
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(decode_kernel<D, NREP, U>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return e;
+        attr_set = true;
+    }
+    decode_kernel<D, NREP, U><<<grid, kDecThreads, smem, st>>>(p);
     return cudaGetLastError();
 }
 
