@@ -7,7 +7,7 @@ import os
 import threading
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, 'libnats_b200.so')
+LIB_PATH = os.environ.get('NATS_B200_LIB') or os.path.join(_HERE, 'libnats_b200.so')   # override: a differently built library
 
 _c = ctypes
 _P, _I, _F, _SZ = _c.c_void_p, _c.c_int, _c.c_float, _c.c_size_t

@@ -2,19 +2,30 @@
 //
 // One block owns kSeg consecutive tokens of the *logical* sequence of one (batch, kv-head):
 //     [ valid ring slots | kept tokens [SW,len) | tokens of the unfinished chunk [T0,T0+fill) | the new token ]
-// A K or V row (D bf16) is read once, by D/8 lanes with one 16-byte load each, and serves all query heads of the
-// group; dot products are reduced across those lanes with a reduce-scatter butterfly so that each lane finishes one
-// (row, head) score, applies the online softmax to it and broadcasts the probability back for the P.V update.
+// and its four warps take 16-token tiles of it in turn.  A tile's K and V rows travel global -> shared memory with
+// cp.async (16 bytes per lane, bypassing L1) through a per-warp ring of kDecStages tiles, so two tiles are in flight
+// while one is consumed and the bytes in flight cost no registers.  All query heads of the group are served by the one
+// read: S = Q.K^T runs as mma.sync m16n8k16 with the (up to 8) query heads as the M rows and 8 tokens as N; the
+// score fragments are exactly the A fragments of O += P.V, so P never leaves registers.  The instruction count per byte
+// is then small enough that the kernel is limited by HBM, not by issue slots.
 // Blocks of a (batch, kv-head) leave partial (max, sum, acc) in the workspace; the block that arrives last combines
 // them (an atomic ticket, nobody waits).  The block owning the last logical token also appends it to the cache.
 #include "common.cuh"
 
 namespace nats {
 
-constexpr int kSeg = 512;          // logical tokens per block
+#ifndef NATS_DEC_SEG
+#define NATS_DEC_SEG 1024
+#endif
+#ifndef NATS_DEC_STAGES
+#define NATS_DEC_STAGES 3
+#endif
+constexpr int kSeg = NATS_DEC_SEG;          // logical tokens per block
+constexpr int kDecStages = NATS_DEC_STAGES; // ring depth per warp
 constexpr int kDecThreads = 128;
 constexpr int kDecWarps = kDecThreads / 32;
-constexpr int kDecStages = 3;       // ring depth per warp: two iterations of loads in flight while one is consumed
+constexpr int kTileTok = 16;                // tokens per warp tile
+constexpr int kMaxRep = 8;                  // query heads per kv-head the fragment rows cover (rows 8..15 stay zero)
 
 struct DecodeParams {
     const __nv_bfloat16* q;        // [B,Hq,1,D]
@@ -28,50 +39,59 @@ struct DecodeParams {
     const long long* size_local;
     const int32_t* state;          // [0] = T0
     int32_t* counters;             // [B*Hkv]   (workspace)
-    float* partials;               // [B*Hkv, max_splits, NREP, D+2]   (workspace)
-    int Hq, Hkv, Lcap, SW, fill, max_splits;
+    float* partials;               // [B*Hkv, max_splits, nrep, D+2]   (workspace)
+    int Hq, Hkv, nrep, Lcap, SW, fill, max_splits;
     float scale_log2;              // sm_scale * log2(e)
 };
-
-__device__ __forceinline__ void unpack8(const uint4& w, float (&f)[8]) {
-    f[0] = __uint_as_float(w.x << 16); f[1] = __uint_as_float(w.x & 0xffff0000u);
-    f[2] = __uint_as_float(w.y << 16); f[3] = __uint_as_float(w.y & 0xffff0000u);
-    f[4] = __uint_as_float(w.z << 16); f[5] = __uint_as_float(w.z & 0xffff0000u);
-    f[6] = __uint_as_float(w.w << 16); f[7] = __uint_as_float(w.w & 0xffff0000u);
-}
 
 __device__ __forceinline__ float fast_exp2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
-
 // 16-byte asynchronous global -> shared copy that bypasses L1; with valid == false nothing is read and zeros are written
-__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc, bool valid) {
-    const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
+__device__ __forceinline__ void cp_async16(uint32_t smem_dst, const void* gsrc, bool valid) {
     const int n = valid ? 16 : 0;
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(gsrc), "r"(n) : "memory");
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_dst), "l"(gsrc), "r"(n) : "memory");
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
-template <int D, int NREP, int U>
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t (&r)[4]) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t (&r)[4]) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+// D (16x8, fp32) += A (16x16, bf16, row) * B (16x8, bf16, col)
+__device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack2_bf16(float lo, float hi) {
+    uint32_t r;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+
+template <int D>
 __global__ void __launch_bounds__(kDecThreads) decode_kernel(const DecodeParams p) {
-    constexpr int TPR = D / 8;                       // lanes per row
-    constexpr int RPW = 32 / TPR;                    // rows per warp per pass
-    constexpr int V = U * NREP;                      // scores per lane group and iteration
-    constexpr bool FAST = (V % TPR == 0) && (V / TPR <= NREP);
-    constexpr int R = FAST ? V / TPR : V;            // scores finished by one lane
-    constexpr int ROWS_IT = kDecWarps * RPW * U;
-    constexpr int G = kDecWarps * RPW;               // lane groups per block
+    constexpr int ROWB = D * 2;                      // bytes of a K or V row
+    constexpr int CHUNKS = ROWB / 16;                // 16-byte chunks per row: 16 (D = 128) or 8 (D = 64)
+    constexpr int TILE_BYTES = kTileTok * ROWB;      // one tile of K (and as much again of V)
+    constexpr int STAGE_BYTES = 2 * TILE_BYTES;
+    constexpr int CP_PER_LANE = kTileTok * CHUNKS / 32;   // cp.async per lane for one of K / V
+    constexpr int ROWS_PER_CP = 32 / CHUNKS;         // rows one warp-wide cp.async covers
     constexpr unsigned FULL = 0xffffffffu;
     const float NEG_INF = -INFINITY;
 
     const int seg = blockIdx.x, hkv = blockIdx.y, b = blockIdx.z;
     const int bh = b * p.Hkv + hkv;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int j = lane % TPR, grp = lane / TPR;
+    const int nrep = p.nrep;
     const int len = (int)(p.size_global[bh] + p.size_local[bh]);
     const int T0 = p.state[0];
     const int Ltot = len + p.fill + 1;
@@ -79,237 +99,189 @@ __global__ void __launch_bounds__(kDecThreads) decode_kernel(const DecodeParams 
     if (seg >= nsplit) return;
     const int r0 = seg * kSeg, r1 = min(Ltot, r0 + kSeg);
 
-    // Dynamic shared memory: per warp a ring of kDecStages stages; a stage holds, for each of the U passes, the 16 bytes of
-    // K and of V every lane has asked for (cp.async), so the bytes in flight do not occupy registers.  Each lane only ever
-    // reads back what it copied itself, so cp.async.wait_group is the only synchronisation.  After the main loop the
-    // same memory holds the per-lane-group partial results that are combined across the block.
-    extern __shared__ __align__(16) uint8_t dsm[];
-    constexpr int STAGE_BYTES = U * 2 * 32 * 16;
-    constexpr int RING_BYTES = kDecWarps * kDecStages * STAGE_BYTES;
-    constexpr int COMBINE_BYTES = G * NREP * (D + 2) * 4;
-    static_assert(COMBINE_BYTES <= RING_BYTES, "combine scratch must fit into the ring");
-    uint8_t* ring = dsm + warp * kDecStages * STAGE_BYTES + lane * 16;
-    float (*s_acc)[NREP][D] = reinterpret_cast<float (*)[NREP][D]>(dsm);
-    float (*s_m)[NREP] = reinterpret_cast<float (*)[NREP]>(dsm + G * NREP * D * 4);
-    float (*s_l)[NREP] = reinterpret_cast<float (*)[NREP]>(dsm + G * NREP * (D + 1) * 4);
+    extern __shared__ __align__(128) uint8_t dsm[];
     __shared__ uint8_t s_ring_ok[kSeg];
     __shared__ int s_last;
+    // after the main loop the ring memory holds the per-warp partial results
+    float (*s_acc)[kMaxRep][D] = reinterpret_cast<float (*)[kMaxRep][D]>(dsm);
+    float (*s_m)[kMaxRep] = reinterpret_cast<float (*)[kMaxRep]>(dsm + kDecWarps * kMaxRep * D * 4);
+    float (*s_l)[kMaxRep] = reinterpret_cast<float (*)[kMaxRep]>(dsm + kDecWarps * kMaxRep * (D + 1) * 4);
+    static_assert(kDecWarps * kMaxRep * (D + 2) * 4 <= kDecWarps * kDecStages * STAGE_BYTES, "combine scratch must fit into the ring");
 
-    const size_t row_elems = (size_t)D;
-    const __nv_bfloat16* ck = p.ck + (size_t)bh * p.Lcap * row_elems;
-    const __nv_bfloat16* cv = p.cv + (size_t)bh * p.Lcap * row_elems;
+    const __nv_bfloat16* ck = p.ck + (size_t)bh * p.Lcap * D;
+    const __nv_bfloat16* cv = p.cv + (size_t)bh * p.Lcap * D;
     const uint8_t* valid = p.valid + (size_t)bh * p.Lcap;
-    const __nv_bfloat16* kn = p.k_new + (size_t)bh * row_elems;
-    const __nv_bfloat16* vn = p.v_new + (size_t)bh * row_elems;
+    const __nv_bfloat16* kn = p.k_new + (size_t)bh * D;
+    const __nv_bfloat16* vn = p.v_new + (size_t)bh * D;
 
     if (r0 < p.SW) {
         for (int i = tid; i < kSeg; i += kDecThreads) s_ring_ok[i] = (r0 + i < p.SW) ? valid[r0 + i] : 1;
     }
     // the block that owns the last logical token appends it (nobody reads that cache row in this launch)
-    if (r1 == Ltot && warp == 0 && grp == 0) {
-        const size_t dst = (size_t)(T0 + p.fill) * row_elems + j * 8;
-        st16(p.ck + (size_t)bh * p.Lcap * row_elems + dst, ld16(kn + j * 8));
-        st16(p.cv + (size_t)bh * p.Lcap * row_elems + dst, ld16(vn + j * 8));
-        if (j == 0) p.valid[(size_t)bh * p.Lcap + T0 + p.fill] = 1;
+    if (r1 == Ltot && warp == 0 && lane < CHUNKS) {
+        const size_t dst = ((size_t)bh * p.Lcap + T0 + p.fill) * D + lane * 8;
+        st16(p.ck + dst, ld16(kn + lane * 8));
+        st16(p.cv + dst, ld16(vn + lane * 8));
+        if (lane == 0) p.valid[(size_t)bh * p.Lcap + T0 + p.fill] = 1;
     }
-    // query fragments: this lane's 8 dims of every head of the group, pre-scaled
-    float q[NREP][8];
+    // Q as A fragments (rows = query heads of the group, 16 dims per k-step); rows >= nrep and rows 8..15 are zero
+    const int hrow = lane >> 2, quad = lane & 3;
+    uint32_t qa[D / 16][2];
+    {
+        const __nv_bfloat16* qrow = p.q + ((size_t)b * p.Hq + (size_t)hkv * nrep + hrow) * D;
 #pragma unroll
-    for (int h = 0; h < NREP; ++h) {
-        const uint4 w = ld16(p.q + ((size_t)b * p.Hq + (size_t)hkv * NREP + h) * row_elems + j * 8);
-        unpack8(w, q[h]);
-#pragma unroll
-        for (int d = 0; d < 8; ++d) q[h][d] *= p.scale_log2;
+        for (int ks = 0; ks < D / 16; ++ks) {
+            qa[ks][0] = hrow < nrep ? *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + quad * 2) : 0u;
+            qa[ks][1] = hrow < nrep ? *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 8 + quad * 2) : 0u;
+        }
     }
     if (r0 < p.SW) __syncthreads();
 
-    float acc[NREP][8];
-#pragma unroll
-    for (int h = 0; h < NREP; ++h)
-#pragma unroll
-        for (int d = 0; d < 8; ++d) acc[h][d] = 0.f;
-    float m_own[R], l_own[R];
-#pragma unroll
-    for (int r = 0; r < R; ++r) { m_own[r] = NEG_INF; l_own[r] = 0.f; }
+    const uint32_t ring = (uint32_t)__cvta_generic_to_shared(dsm) + warp * kDecStages * STAGE_BYTES;
+    const int n_tiles = (r1 - r0 + kTileTok - 1) / kTileTok;            // tiles of this block
+    const int my_tiles = (n_tiles - warp + kDecWarps - 1) / kDecWarps;   // tiles warp, warp + 4, ... are this warp's
 
-    // issue the copies of iteration `it` into its ring stage (rows that do not exist or are invalid are zero-filled)
+    // issue the copies of this warp's it-th tile: row r of the tile, chunk c goes to r*ROWB + ((c ^ (r & 7)) * 16)
     auto issue = [&](int it) {
-        const int base = r0 + it * ROWS_IT;
-        uint8_t* dst = ring + (it % kDecStages) * STAGE_BYTES;
+        const int i0 = r0 + (it * kDecWarps + warp) * kTileTok;
+        const uint32_t dst = ring + (it % kDecStages) * STAGE_BYTES;
+        const int c = lane % CHUNKS, rsub = lane / CHUNKS;
+        if (i0 + kTileTok <= len) {                      // whole tile inside ring + kept tokens: logical == physical
+            const __nv_bfloat16* kp = ck + (size_t)i0 * D + c * 8;
+            const __nv_bfloat16* vp = cv + (size_t)i0 * D + c * 8;
 #pragma unroll
-        for (int u = 0; u < U; ++u) {
-            const int i = base + u * (kDecWarps * RPW) + warp * RPW + grp;
-            bool ok = i < r1;
-            const __nv_bfloat16 *kp = ck, *vpp = cv;
-            if (ok) {
-                if (i < p.SW) { ok = s_ring_ok[i - r0] != 0; kp = ck + (size_t)i * row_elems; vpp = cv + (size_t)i * row_elems; }
-                else if (i < len) { kp = ck + (size_t)i * row_elems; vpp = cv + (size_t)i * row_elems; }
-                else if (i < len + p.fill) { const size_t ph = (size_t)(T0 + (i - len)); kp = ck + ph * row_elems; vpp = cv + ph * row_elems; }
-                else { kp = kn; vpp = vn; }
+            for (int x = 0; x < CP_PER_LANE; ++x) {
+                const int r = x * ROWS_PER_CP + rsub;
+                const uint32_t off = r * ROWB + ((c ^ (r & 7)) << 4);
+                cp_async16(dst + off, kp + (size_t)r * D, true);
+                cp_async16(dst + TILE_BYTES + off, vp + (size_t)r * D, true);
             }
-            cp_async16(dst + (u * 2 + 0) * 512, kp + j * 8, ok);
-            cp_async16(dst + (u * 2 + 1) * 512, vpp + j * 8, ok);
+        } else {
+#pragma unroll
+            for (int x = 0; x < CP_PER_LANE; ++x) {
+                const int r = x * ROWS_PER_CP + rsub;
+                const int i = i0 + r;
+                const bool ok = i < r1;
+                const __nv_bfloat16 *kp = ck, *vp = cv;
+                if (ok) {
+                    if (i < len) { kp = ck + (size_t)i * D; vp = cv + (size_t)i * D; }
+                    else if (i < len + p.fill) { const size_t ph = (size_t)(T0 + (i - len)); kp = ck + ph * D; vp = cv + ph * D; }
+                    else { kp = kn; vp = vn; }
+                }
+                const uint32_t off = r * ROWB + ((c ^ (r & 7)) << 4);
+                cp_async16(dst + off, kp + c * 8, ok);
+                cp_async16(dst + TILE_BYTES + off, vp + c * 8, ok);
+            }
         }
     };
-    const int n_it = (r1 - r0 + ROWS_IT - 1) / ROWS_IT;
+
+    float oacc[D / 8][4];
+#pragma unroll
+    for (int n = 0; n < D / 8; ++n) { oacc[n][0] = oacc[n][1] = oacc[n][2] = oacc[n][3] = 0.f; }
+    float m_run = NEG_INF, l_run = 0.f;              // of query head `hrow`; l is this lane's share until the end
+
 #pragma unroll
     for (int it = 0; it < kDecStages - 1; ++it) {
-        if (it < n_it) issue(it);
+        if (it < my_tiles) issue(it);
         cp_async_commit();
     }
-    for (int it = 0; it < n_it; ++it) {
-        if (it + kDecStages - 1 < n_it) issue(it + kDecStages - 1);
+    for (int it = 0; it < my_tiles; ++it) {
+        __syncwarp();                                // every lane is done reading the stage that is refilled now
+        if (it + kDecStages - 1 < my_tiles) issue(it + kDecStages - 1);
         cp_async_commit();
         cp_async_wait<kDecStages - 1>();
-        const int base = r0 + it * ROWS_IT;
-        const uint8_t* src = ring + (it % kDecStages) * STAGE_BYTES;
-        uint4 kq[U], vq[U];
-        unsigned okmask = 0;
-#pragma unroll
-        for (int u = 0; u < U; ++u) {
-            const int i = base + u * (kDecWarps * RPW) + warp * RPW + grp;
-            const bool ok = i < r1 && (i >= p.SW || s_ring_ok[i - r0] != 0);
-            okmask |= (ok ? 1u : 0u) << u;
-            kq[u] = *reinterpret_cast<const uint4*>(src + (u * 2 + 0) * 512);
-            vq[u] = *reinterpret_cast<const uint4*>(src + (u * 2 + 1) * 512);
+        __syncwarp();                                // ... and sees the other lanes' copies of the stage consumed now
+        const int i0 = r0 + (it * kDecWarps + warp) * kTileTok;
+        const uint32_t sk = ring + (it % kDecStages) * STAGE_BYTES, sv = sk + TILE_BYTES;
+        unsigned vmask = 0xffffu;                    // which of the 16 tokens exist and are valid
+        if (i0 < p.SW || i0 + kTileTok > r1) {
+            bool ok = false;
+            if (lane < kTileTok) {
+                const int i = i0 + lane;
+                ok = i < r1 && (i >= p.SW || s_ring_ok[i - r0] != 0);
+            }
+            vmask = __ballot_sync(FULL, ok) & 0xffffu;
         }
-
-        float part[V];
+        // ---- S[heads x 16 tokens] = Q . K^T ----
+        float sc[2][4];
 #pragma unroll
-        for (int u = 0; u < U; ++u) {
-            float kf[8];
-            unpack8(kq[u], kf);
+        for (int nt = 0; nt < 2; ++nt) {
+            sc[nt][0] = sc[nt][1] = sc[nt][2] = sc[nt][3] = 0.f;
+            const int r = nt * 8 + (lane & 7);
 #pragma unroll
-            for (int h = 0; h < NREP; ++h) {
-                float s = 0.f;
-#pragma unroll
-                for (int d = 0; d < 8; ++d) s = fmaf(q[h][d], kf[d], s);
-                part[u * NREP + h] = s;
-            }
-        }
-        float p_all[V], alpha[NREP];
-        if constexpr (FAST) {
-            // reduce-scatter over the TPR lanes of the row: lane j ends with the totals of scores j*R .. j*R+R-1
-            int cnt = V;
-#pragma unroll
-            for (int off = TPR / 2; off >= 1; off >>= 1) {
-                cnt >>= 1;
-                const bool upper = (j & off) != 0;
-#pragma unroll
-                for (int i = 0; i < V / 2; ++i) {
-                    if (i < cnt) {
-                        const float send = upper ? part[i] : part[i + cnt];
-                        const float keep = upper ? part[i + cnt] : part[i];
-                        part[i] = keep + __shfl_xor_sync(FULL, send, off);
-                    }
-                }
-            }
-            float pr[R], al[R];
-#pragma unroll
-            for (int r = 0; r < R; ++r) {
-                const int idx = j * R + r;
-                const int u = idx / NREP;
-                float s = ((okmask >> u) & 1u) ? part[r] : NEG_INF;
-                float mt = s;                       // max over the U rows of this iteration, same head
-#pragma unroll
-                for (int off = NREP / R; off < TPR; off <<= 1) mt = fmaxf(mt, __shfl_xor_sync(FULL, mt, off));
-                const float m_new = fmaxf(m_own[r], mt);
-                const float m_use = (m_new == NEG_INF) ? 0.f : m_new;
-                al[r] = fast_exp2(m_own[r] - m_use);
-                pr[r] = fast_exp2(s - m_use);
-                l_own[r] = l_own[r] * al[r] + pr[r];
-                m_own[r] = m_new;
-            }
-            const int gbase = grp * TPR;
-#pragma unroll
-            for (int h = 0; h < NREP; ++h) alpha[h] = __shfl_sync(FULL, al[h % R], gbase + h / R);
-#pragma unroll
-            for (int i = 0; i < V; ++i) p_all[i] = __shfl_sync(FULL, pr[i % R], gbase + i / R);
-        } else {
-            // all-reduce every score; every lane then runs the same softmax update (R == V)
-#pragma unroll
-            for (int i = 0; i < V; ++i)
-#pragma unroll
-                for (int off = TPR / 2; off >= 1; off >>= 1) part[i] += __shfl_xor_sync(FULL, part[i], off);
-#pragma unroll
-            for (int h = 0; h < NREP; ++h) {
-                float mt = NEG_INF;
-#pragma unroll
-                for (int u = 0; u < U; ++u) {
-                    if (!((okmask >> u) & 1u)) part[u * NREP + h] = NEG_INF;
-                    mt = fmaxf(mt, part[u * NREP + h]);
-                }
-                const float m_new = fmaxf(m_own[h], mt);        // slots 0..NREP-1 of m_own / l_own are per head here
-                const float m_use = (m_new == NEG_INF) ? 0.f : m_new;
-                alpha[h] = fast_exp2(m_own[h] - m_use);
-                float ls = 0.f;
-#pragma unroll
-                for (int u = 0; u < U; ++u) {
-                    p_all[u * NREP + h] = fast_exp2(part[u * NREP + h] - m_use);
-                    ls += p_all[u * NREP + h];
-                }
-                l_own[h] = l_own[h] * alpha[h] + ls;
-                m_own[h] = m_new;
+            for (int kp = 0; kp < D / 32; ++kp) {
+                uint32_t kb[4];
+                const int chunk = kp * 4 + (lane >> 3);
+                ldmatrix_x4(sk + r * ROWB + ((chunk ^ (r & 7)) << 4), kb);
+                mma_bf16(sc[nt], qa[2 * kp][0], 0u, qa[2 * kp][1], 0u, kb[0], kb[1]);
+                mma_bf16(sc[nt], qa[2 * kp + 1][0], 0u, qa[2 * kp + 1][1], 0u, kb[2], kb[3]);
             }
         }
+        // ---- online softmax of head `hrow` over the 4 scores this lane holds (tokens nt*8 + quad*2 + {0,1}) ----
+        float s[4];
 #pragma unroll
-        for (int h = 0; h < NREP; ++h)
+        for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
-            for (int d = 0; d < 8; ++d) acc[h][d] *= alpha[h];
+            for (int e = 0; e < 2; ++e) {
+                const int t = nt * 8 + quad * 2 + e;
+                s[nt * 2 + e] = ((vmask >> t) & 1u) ? sc[nt][e] * p.scale_log2 : NEG_INF;
+            }
+        float mt = fmaxf(fmaxf(s[0], s[1]), fmaxf(s[2], s[3]));
+        mt = fmaxf(mt, __shfl_xor_sync(FULL, mt, 1));
+        mt = fmaxf(mt, __shfl_xor_sync(FULL, mt, 2));
+        const float m_new = fmaxf(m_run, mt);
+        const float mu = (m_new == NEG_INF) ? 0.f : m_new;
+        const float alpha = fast_exp2(m_run - mu);
+        const float p0 = fast_exp2(s[0] - mu), p1 = fast_exp2(s[1] - mu), p2 = fast_exp2(s[2] - mu), p3 = fast_exp2(s[3] - mu);
+        l_run = l_run * alpha + (p0 + p1) + (p2 + p3);
+        m_run = m_new;
+        if (__any_sync(FULL, alpha != 1.f)) {
 #pragma unroll
-        for (int u = 0; u < U; ++u) {
-            float vf[8];
-            unpack8(vq[u], vf);
+            for (int n = 0; n < D / 8; ++n) { oacc[n][0] *= alpha; oacc[n][1] *= alpha; }
+        }
+        const uint32_t pa0 = pack2_bf16(p0, p1), pa2 = pack2_bf16(p2, p3);
+        // ---- O[heads x D] += P . V ----
 #pragma unroll
-            for (int h = 0; h < NREP; ++h)
-#pragma unroll
-                for (int d = 0; d < 8; ++d) acc[h][d] = fmaf(p_all[u * NREP + h], vf[d], acc[h][d]);
+        for (int np = 0; np < D / 16; ++np) {
+            uint32_t vb[4];
+            const int r = ((lane >> 3) & 1) * 8 + (lane & 7);
+            const int chunk = np * 2 + (lane >> 4);
+            ldmatrix_x4_trans(sv + r * ROWB + ((chunk ^ (r & 7)) << 4), vb);
+            mma_bf16(oacc[2 * np], pa0, 0u, pa2, 0u, vb[0], vb[1]);
+            mma_bf16(oacc[2 * np + 1], pa0, 0u, pa2, 0u, vb[2], vb[3]);
         }
     }
 
-    // ---- combine the lane groups of this block (the ring is drained: every copy was waited for) ----
+    // ---- combine the warps of this block (the ring is drained first: its memory is reused) ----
     cp_async_wait<0>();
     __syncthreads();
-    const int g = warp * RPW + grp;
-    if constexpr (FAST) {
+    l_run += __shfl_xor_sync(FULL, l_run, 1);
+    l_run += __shfl_xor_sync(FULL, l_run, 2);
+    if (hrow < nrep) {
+        if (quad == 0) { s_m[warp][hrow] = m_run; s_l[warp][hrow] = l_run; }
 #pragma unroll
-        for (int r = 0; r < R; ++r) {
-            float l = l_own[r];
-#pragma unroll
-            for (int off = NREP / R; off < TPR; off <<= 1) l += __shfl_xor_sync(FULL, l, off);
-            const int idx = j * R + r;
-            if (idx < NREP) { s_m[g][idx] = m_own[r]; s_l[g][idx] = l; }
-        }
-    } else {
-        if (j == 0) {
-#pragma unroll
-            for (int h = 0; h < NREP; ++h) { s_m[g][h] = m_own[h]; s_l[g][h] = l_own[h]; }
-        }
-    }
-#pragma unroll
-    for (int h = 0; h < NREP; ++h) {
-        *reinterpret_cast<float4*>(&s_acc[g][h][j * 8]) = make_float4(acc[h][0], acc[h][1], acc[h][2], acc[h][3]);
-        *reinterpret_cast<float4*>(&s_acc[g][h][j * 8 + 4]) = make_float4(acc[h][4], acc[h][5], acc[h][6], acc[h][7]);
+        for (int n = 0; n < D / 8; ++n)
+            *reinterpret_cast<float2*>(&s_acc[warp][hrow][n * 8 + quad * 2]) = make_float2(oacc[n][0], oacc[n][1]);
     }
     __syncthreads();
     constexpr int PSTRIDE = D + 2;
-    float* part_out = p.partials + ((size_t)bh * p.max_splits + seg) * NREP * PSTRIDE;
-    for (int idx = tid; idx < NREP * D; idx += kDecThreads) {
+    float* part_out = p.partials + ((size_t)bh * p.max_splits + seg) * nrep * PSTRIDE;
+    for (int idx = tid; idx < nrep * D; idx += kDecThreads) {
         const int h = idx / D, d = idx % D;
         float mf = NEG_INF;
 #pragma unroll
-        for (int gg = 0; gg < G; ++gg) mf = fmaxf(mf, s_m[gg][h]);
+        for (int w = 0; w < kDecWarps; ++w) mf = fmaxf(mf, s_m[w][h]);
         const float mu = (mf == NEG_INF) ? 0.f : mf;
         float a = 0.f, l = 0.f;
 #pragma unroll
-        for (int gg = 0; gg < G; ++gg) {
-            const float w = fast_exp2(s_m[gg][h] - mu);
-            a = fmaf(s_acc[gg][h][d], w, a);
-            l = fmaf(s_l[gg][h], w, l);
+        for (int w = 0; w < kDecWarps; ++w) {
+            const float wgt = fast_exp2(s_m[w][h] - mu);
+            a = fmaf(s_acc[w][h][d], wgt, a);
+            l = fmaf(s_l[w][h], wgt, l);
         }
         if (nsplit == 1) {
             const float inv = l > 0.f ? 1.f / l : 0.f;
-            p.o[((size_t)b * p.Hq + (size_t)hkv * NREP + h) * D + d] = __float2bfloat16_rn(a * inv);
+            p.o[((size_t)b * p.Hq + (size_t)hkv * nrep + h) * D + d] = __float2bfloat16_rn(a * inv);
         } else {
             part_out[h * PSTRIDE + d] = a;
             if (d == 0) { part_out[h * PSTRIDE + D] = mf; part_out[h * PSTRIDE + D + 1] = l; }
@@ -326,37 +298,35 @@ __global__ void __launch_bounds__(kDecThreads) decode_kernel(const DecodeParams 
     __syncthreads();
     if (!s_last) return;
     __threadfence();
-    const float* parts = p.partials + (size_t)bh * p.max_splits * NREP * PSTRIDE;
-    for (int idx = tid; idx < NREP * D; idx += kDecThreads) {
+    const float* parts = p.partials + (size_t)bh * p.max_splits * nrep * PSTRIDE;
+    for (int idx = tid; idx < nrep * D; idx += kDecThreads) {
         const int h = idx / D, d = idx % D;
         float mf = NEG_INF;
-        for (int s = 0; s < nsplit; ++s) mf = fmaxf(mf, __ldcg(parts + ((size_t)s * NREP + h) * PSTRIDE + D));
+        for (int s = 0; s < nsplit; ++s) mf = fmaxf(mf, __ldcg(parts + ((size_t)s * nrep + h) * PSTRIDE + D));
         const float mu = (mf == NEG_INF) ? 0.f : mf;
         float a = 0.f, l = 0.f;
         for (int s = 0; s < nsplit; ++s) {
-            const float* ps = parts + ((size_t)s * NREP + h) * PSTRIDE;
-            const float w = fast_exp2(__ldcg(ps + D) - mu);
-            a = fmaf(__ldcg(ps + d), w, a);
-            l = fmaf(__ldcg(ps + D + 1), w, l);
+            const float* ps = parts + ((size_t)s * nrep + h) * PSTRIDE;
+            const float wgt = fast_exp2(__ldcg(ps + D) - mu);
+            a = fmaf(__ldcg(ps + d), wgt, a);
+            l = fmaf(__ldcg(ps + D + 1), wgt, l);
         }
         const float inv = l > 0.f ? 1.f / l : 0.f;
-        p.o[((size_t)b * p.Hq + (size_t)hkv * NREP + h) * D + d] = __float2bfloat16_rn(a * inv);
+        p.o[((size_t)b * p.Hq + (size_t)hkv * nrep + h) * D + d] = __float2bfloat16_rn(a * inv);
     }
     if (tid == 0) p.counters[bh] = 0;
 }
 
-template <int D, int NREP>
+template <int D>
 static cudaError_t launch_decode(const DecodeParams& p, dim3 grid, cudaStream_t st) {
-    constexpr int TPR = D / 8;
-    constexpr int U = (NREP * 4 >= TPR) ? 4 : ((NREP * 8 >= TPR) ? 8 : 4);
-    constexpr int smem = kDecWarps * kDecStages * U * 2 * 32 * 16;
+    constexpr int smem = kDecWarps * kDecStages * 2 * kTileTok * D * 2;
     static bool attr_set = false;
     if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(decode_kernel<D, NREP, U>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        cudaError_t e = cudaFuncSetAttribute(decode_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return e;
         attr_set = true;
     }
-    decode_kernel<D, NREP, U><<<grid, kDecThreads, smem, st>>>(p);
+    decode_kernel<D><<<grid, kDecThreads, smem, st>>>(p);
     return cudaGetLastError();
 }
 
@@ -391,8 +361,9 @@ extern "C" __attribute__((visibility("default"))) int nats_b200_decode_fwd(const
                    "length bound %d (+ fill %d) does not fit the cache capacity %d", max_len_bound, fill, Lcap);
     NATS_CHECK_ARG(B <= 65535 && Hkv <= 65535, "B and Hkv must not exceed 65535");
     const int nrep = Hq / Hkv;
-    if (!(D == 64 || D == 128) || !(nrep == 1 || nrep == 2 || nrep == 4 || nrep == 8))
-        return fail(NATS_ERR_UNSUPPORTED, "decode supports head_dim {64,128} and group size {1,2,4,8}; got %d, %d", D, nrep);
+    if (!(D == 64 || D == 128) || nrep > kMaxRep)
+        return fail(NATS_ERR_UNSUPPORTED, "decode supports head_dim {64,128} and up to %d query heads per kv-head; got %d, %d",
+                    kMaxRep, D, nrep);
     const int max_len = max_len_bound + C;
     const size_t need = nats_b200_decode_workspace_bytes(B, Hq, Hkv, D, max_len);
     if (workspace_bytes < need) return fail(NATS_ERR_WORKSPACE, "decode workspace: %zu bytes given, %zu needed", workspace_bytes, need);
@@ -402,17 +373,11 @@ extern "C" __attribute__((visibility("default"))) int nats_b200_decode_fwd(const
     p.size_global = (const long long*)d_size_global; p.size_local = (const long long*)d_size_local; p.state = d_state;
     p.counters = (int32_t*)d_workspace;
     p.partials = (float*)((uint8_t*)d_workspace + decode_counter_bytes(B, Hkv));
-    p.Hq = Hq; p.Hkv = Hkv; p.Lcap = Lcap; p.SW = SW; p.fill = fill;
+    p.Hq = Hq; p.Hkv = Hkv; p.nrep = nrep; p.Lcap = Lcap; p.SW = SW; p.fill = fill;
     p.max_splits = decode_max_splits(max_len);
     p.scale_log2 = sm_scale * 1.4426950408889634f;
     dim3 grid(cdiv(max_len_bound + fill + 1, kSeg), Hkv, B);
-    cudaStream_t st = (cudaStream_t)stream;
-    cudaError_t e;
-#define NATS_DEC(DD, RR) if (D == DD && nrep == RR) e = launch_decode<DD, RR>(p, grid, st); else
-    NATS_DEC(128, 1) NATS_DEC(128, 2) NATS_DEC(128, 4) NATS_DEC(128, 8)
-    NATS_DEC(64, 1) NATS_DEC(64, 2) NATS_DEC(64, 4) NATS_DEC(64, 8)
-    e = cudaErrorInvalidValue;
-#undef NATS_DEC
+    cudaError_t e = (D == 64) ? launch_decode<64>(p, grid, (cudaStream_t)stream) : launch_decode<128>(p, grid, (cudaStream_t)stream);
     NATS_CHECK_CUDA(e);
     return NATS_OK;
 }
