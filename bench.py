@@ -46,6 +46,17 @@ def load_peaks():
     return dict(FALLBACK_PEAKS, _source='fallback')
 
 
+def load_traffic():
+    """DRAM bytes per launch measured with ncu (profiles/ncu_traffic.json), or None where no capture is recorded."""
+    path = os.path.join(ROOT, 'profiles', 'ncu_traffic.json')
+    try:
+        with open(path) as f:
+            d = json.load(f)
+        return {k: v.get('bytes_per_launch') for k, v in d.items() if isinstance(v, dict)}
+    except (OSError, ValueError):
+        return {}
+
+
 # ---------------------------------------------------------------------------------------------- synthetic inputs
 def role_bias(p_global, p_local):
     """Bias of the 3-way N(0,1) role logits that yields the requested global / local share (rest sliding)."""
@@ -281,6 +292,7 @@ def main():
     device = torch.device('cuda', local_rank)
     torch.cuda.set_device(device)
     peaks = load_peaks()
+    traffic = load_traffic() if args.case == 'full' else {}
 
     def barrier():
         if world > 1:
@@ -375,7 +387,7 @@ def main():
                       config='B64 x 32q/8kv heads, head_dim 128, retained 2k-6k per (sequence, kv-head) + 1024-slot ring '
                              '(80 % valid), chunk 128, one role per completed chunk',
                       roofline=dict(bound='hbm', achieved=gbs, peak=peaks['hbm_gbs'], unit='GB/s', frac=gbs / peaks['hbm_gbs'],
-                                    traffic=None, bytes_per_step=r['kv_bytes_per_step'], of=peaks['_source']))
+                                    traffic=traffic.get('decode_kernel'), bytes_per_step=r['kv_bytes_per_step'], of=peaks['_source']))
         if world > 1:      # NCCL only here: gather the last step's outputs of all ranks
             outs = [torch.empty_like(r['out']) for _ in range(world)]
             dist.all_gather(outs, r['out'])
@@ -396,7 +408,7 @@ def main():
                     data='synthetic', config=config, clocks=clocks,
                     e2e=dict(value=e2e_value, unit='TFLOP/s', h2d_bytes_per_step=h2d, d2h_bytes_per_step=d2h),
                     gpu_launches=4 * args.steps,
-                    roofline=dict(bound='tensor', achieved=tf, peak=peak, unit='TFLOP/s', frac=tf / peak, traffic=None,
+                    roofline=dict(bound='tensor', achieved=tf, peak=peak, unit='TFLOP/s', frac=tf / peak, traffic=traffic.get('prefill_kernel'),
                                   kernel='prefill_kernel<128>', ms_per_launch=ms_prefill, of=peaks['_source'] + ' cuBLAS bf16'),
                     kept_tiles=dict(kept=n_kept, causal=n_tiles_causal, skipped_frac=1 - n_kept / n_tiles_causal,
                                     flop_per_step=flops),

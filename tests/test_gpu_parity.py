@@ -337,6 +337,8 @@ DECODE_CASES = [
     dict(B=2, Hq=4, Hkv=2, N=512, D=64, C=8, SW=64, steps=40),          # group of 2
     dict(B=1, Hq=2, Hkv=2, N=5, D=128, C=8, SW=16, steps=30),           # prefill shorter than a chunk
     dict(B=2, Hq=8, Hkv=2, N=3000, D=128, C=128, SW=1024, steps=130),   # several splits per head
+    dict(B=2, Hq=6, Hkv=2, N=700, D=128, C=16, SW=64, steps=40),        # group of 3
+    dict(B=1, Hq=5, Hkv=1, N=2500, D=64, C=32, SW=256, steps=40),       # group of 5, several splits
 ]
 
 
@@ -488,3 +490,85 @@ def test_decode_equals_one_shot_prefill_on_gpu():
         lc.post_update(1)
         err = (o.float() - full[:, :, t:t + 1].float()).abs().max().item()
         assert err <= 2e-2, (i, err)
+
+
+def test_long_context_configuration_131k():
+    """The 131072-token stress configuration (B2, 32/8 heads, window 4096, chunk 128, ~2 % global / 8 % local): kept-tile
+    count against the closed form, spot rows against the blocked fp32 oracle, eviction state against the oracle."""
+    from neuralattentionsearch_b200 import check_status, prefill_attention
+    B, Hq, Hkv, N, D, C, SW = 2, 32, 8, 131072, 128, 128, 4096
+    roles = orc.make_roles(B, Hkv, N // C, 0.02, 0.08, seed=4)
+    g = torch.Generator(device=dev()).manual_seed(4)
+    q = (torch.randn(B, Hq, N, D, generator=g, device=dev()) * 0.5).bfloat16()
+    k = (torch.randn(B, Hkv, N, D, generator=g, device=dev()) * 0.5).bfloat16()
+    v = (torch.randn(B, Hkv, N, D, generator=g, device=dev()) * 0.5).bfloat16()
+    kept = torch.zeros(B, Hkv, dtype=torch.int64, device=dev())
+    o = prefill_attention(q, k, v, torch.from_numpy(roles).to(dev()), C, SW, kept_tiles=kept)
+    check_status(dev())
+    ref_kept = orc.kept_tiles(roles, C, SW, N)
+    assert np.array_equal(kept.cpu().numpy(), ref_kept)
+    n_causal = (N // 128) * (N // 128 + 1) // 2
+    assert 0.80 < 1 - ref_kept.mean() / n_causal < 0.97          # most tiles are skipped
+    for (b, h, lo) in ((0, 0, 0), (1, 3, 65536 + 256), (1, 7, N - 128)):
+        sl = slice(h * 4, h * 4 + 4)
+        ref = orc.prefill_attention(q[b:b + 1, sl, :lo + 128].float().cpu(), k[b:b + 1, h:h + 1, :lo + 128].float().cpu(),
+                                    v[b:b + 1, h:h + 1, :lo + 128].float().cpu(), roles[b:b + 1, h:h + 1, :(lo + 128) // C], C, SW,
+                                    rows=(lo, lo + 128), block=128)
+        # rows before the end of the sequence see the same keys whether or not later chunks exist, except that the oracle
+        # treats its last chunk as global for the next-global index -- which never changes a visible set (it only ends locals)
+        assert_close_attn(o[b:b + 1, sl, lo:lo + 128], ref, f'rows {lo} of ({b},{h})')
+    # eviction of one sequence at this size: index-level state against the oracle (bytes are covered at smaller sizes)
+    lc = run_gpu_cache(dict(B=1, Hkv=Hkv, SW=SW, C=C), roles[:1], k[:1], v[:1])
+    torch.cuda.synchronize()
+    rl = roles[0]
+    n_g = (rl == 0).sum(-1)
+    last_g = np.where(rl == 0, np.arange(N // C), -1).max(-1)
+    n_l = ((rl == 1) & (np.arange(N // C)[None] > last_g[:, None])).sum(-1)
+    assert np.array_equal(lc.size_global_kv.cpu().numpy()[0], SW + C * n_g)
+    assert np.array_equal(lc.size_local_kv.cpu().numpy()[0], C * n_l)
+    lens = SW + C * (n_g + n_l)
+    assert lc.n_ctx_data == lens.max()
+    valid = lc.valid_tokens.cpu().numpy()[0]
+    for h in range(Hkv):
+        assert valid[h, SW:lens[h]].all() and not valid[h, lens[h]:].any()
+        # first and last kept chunk of the head carry the bytes of the right source chunks
+        kept_idx = np.nonzero((rl[h] == 0) | ((rl[h] == 1) & (np.arange(N // C) > last_g[h])))[0]
+        for slot in (0, len(kept_idx) - 1):
+            src = kept_idx[slot] * C
+            assert torch.equal(lc.cache_k[0, h, SW + slot * C:SW + (slot + 1) * C], k[0, h, src:src + C])
+            assert torch.equal(lc.cache_v[0, h, SW + slot * C:SW + (slot + 1) * C], v[0, h, src:src + C])
+
+
+def test_decode_configuration_batch64_ragged():
+    """The decode configuration at full size (batch 64, 32/8 heads, retained 2k-6k per (sequence, kv-head), 1024-slot
+    ring): outputs of sampled (sequence, kv-head) pairs against the fp32 oracle over several steps, a chunk placement included."""
+    import bench
+    d = dict(bench.DECODE)
+    lc = bench.build_decode_cache(d, dev())
+    B, Hq, Hkv, D, C, SW = d['B'], d['Hq'], d['Hkv'], d['D'], d['C'], d['SW']
+    g = torch.Generator(device=dev()).manual_seed(7)
+    pairs = [(0, 0), (17, 3), (63, 7), (40, 5)]
+    lc.chunk_fill_size = C - 3                      # three steps before a chunk completes
+    lc._state[0] = lc._t0_exact                     # unfinished chunk region starts at the common offset
+    t0 = lc._t0_exact
+    tail = (torch.randn(B, Hkv, C - 3, D, generator=g, device=dev()) * 0.5).bfloat16()
+    lc._buf_k[:, :, t0:t0 + C - 3] = tail
+    lc._buf_v[:, :, t0:t0 + C - 3] = tail.flip(-1)
+    lc._buf_valid[:, :, t0:t0 + C - 3] = 1
+    for step in range(6):
+        q1 = (torch.randn(B, Hq, 1, D, generator=g, device=dev()) * 0.5).bfloat16()
+        k1 = (torch.randn(B, Hkv, 1, D, generator=g, device=dev()) * 0.5).bfloat16()
+        v1 = (torch.randn(B, Hkv, 1, D, generator=g, device=dev()) * 0.5).bfloat16()
+        done = lc.chunk_fill_size + 1 == C
+        roles = torch.randint(0, 3, (B, Hkv, 1), generator=g, device=dev()).to(torch.uint8) if done else \
+            torch.zeros(B, Hkv, 1, dtype=torch.uint8, device=dev())
+        lc.update(k1, v1, roles, fused=True)
+        o = lc.decode_attention(q1)
+        torch.cuda.synchronize()
+        n = lc.n_ctx_data + 1                       # the extent the reference's decode mask covers
+        for (b, h) in pairs:
+            mask = lc._buf_valid[b, h, :n].bool().cpu().numpy()[None, None]
+            ref = orc.decode_attention(q1[b:b + 1, h * 4:h * 4 + 4].float().cpu(), lc._buf_k[b:b + 1, h:h + 1, :n].float().cpu().numpy(),
+                                       lc._buf_v[b:b + 1, h:h + 1, :n].float().cpu().numpy(), mask)
+            assert_close_attn(o[b:b + 1, h * 4:h * 4 + 4], ref, f'step {step} pair ({b},{h})')
+        lc.post_update(1)
