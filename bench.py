@@ -352,11 +352,16 @@ def main():
     d2h = ho.numel() * ho.element_size()
     e2e_steps = max(3, min(args.steps, 5))
 
+    from neuralattentionsearch_b200 import HostPrefillPipeline
+    pipe = HostPrefillPipeline(w['B'], w['Hq'], w['Hkv'], w['N'], w['D'], w['C'], w['SW'], device)
+
     def e2e_step():
-        qd, kd, vd = hq.to(device, non_blocking=True), hk.to(device, non_blocking=True), hv.to(device, non_blocking=True)
-        roles.copy_(hroles, non_blocking=True)
-        o, _ = step(qd, kd, vd)
-        ho.copy_(o, non_blocking=True)
+        # the call a user with host-resident tensors makes: pinned q/k/v/roles in, pinned output out; pieces of one
+        # (batch, kv-head) pair are copied in, computed and copied out concurrently; the eviction follows on the device
+        pipe.run(hq, hk, hv, hroles, ho)
+        lc = NAtSChunkLayerCache(w['B'], w['Hkv'], w['SW'], chunk_size=w['C'], device=device)
+        lc.update(pipe.k, pipe.v, pipe.roles)
+        lc.post_update(w['N'])
 
     e2e_step()
     barrier()

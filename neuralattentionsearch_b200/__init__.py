@@ -7,7 +7,7 @@ Public surface (names follow the reference project):
 The CUDA kernels live in libnats_b200.so (C-ABI in include/nats_b200.h); build it with
 ``python -m neuralattentionsearch_b200.build``.
 """
-from .functional import (check_status, nats_attention, nats_chunk_attention, nats_prefill, prefill_attention,  # noqa: F401
+from .functional import (HostPrefillPipeline, check_status, nats_attention, nats_chunk_attention, nats_prefill, prefill_attention,  # noqa: F401
                          roles_from_token_states_info)
 from .cache import NAtSCache, NAtSChunkLayerCache  # noqa: F401
 from .attention import (BaseNAtSChunkAttentionLayer, GPTNAtSChunkAttentionLayer,  # noqa: F401

@@ -96,7 +96,7 @@ def _as_bf16(t: torch.Tensor) -> torch.Tensor:
 
 def prefill_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, roles: torch.Tensor, chunk_size: int,
                       sliding_window: int, sm_scale: float | None = None,
-                      kept_tiles: torch.Tensor | None = None) -> torch.Tensor:
+                      kept_tiles: torch.Tensor | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
     """Role-masked causal attention of a first prefill call.  q [B,Hq,N,D], k/v [B,Hkv,N,D] (cast to bf16 if
     needed), roles uint8 [B,Hkv,ceil(N/C)].  Returns o [B,Hq,N,D] in q's dtype."""
     dev = _need_cuda(q, k, v, roles)
@@ -108,7 +108,9 @@ def prefill_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, roles: 
     if roles.shape != (B, Hkv, nc) or roles.dtype != torch.uint8:
         raise ValueError(f'roles must be uint8 [{B},{Hkv},{nc}], got {roles.dtype} {tuple(roles.shape)}')
     qb, kb, vb = _as_bf16(q), _as_bf16(k), _as_bf16(v)
-    o = torch.empty_like(qb)
+    if out is not None and (out.shape != qb.shape or out.dtype != torch.bfloat16 or not out.is_contiguous()):
+        raise ValueError('out must be a contiguous bf16 tensor shaped like q')
+    o = torch.empty_like(qb) if out is None else out
     lib = _lib.lib()
     nbytes = lib.nats_b200_prefill_workspace_bytes(B, Hkv, N, chunk_size)
     ws = _workspace('prefill', dev, nbytes)
@@ -116,6 +118,67 @@ def prefill_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, roles: 
     _lib.call('nats_b200_prefill_fwd', _p(qb), _p(kb), _p(vb), _p(o), _p(roles.contiguous()), B, Hq, Hkv, N, D,
               chunk_size, sliding_window, scale, _p(ws), ws.numel(), _p(kept_tiles), _p(status_word(dev)), _stream(dev))
     return o if q.dtype == torch.bfloat16 else o.to(q.dtype)
+
+
+class HostPrefillPipeline:
+    """Prefill for callers whose q/k/v live in (pinned) host memory and who want the output back in host memory.
+
+    The (batch, kv-head) pairs are independent, so the work is cut into one piece per pair and pipelined over three
+    streams: host->device copy of piece i+1, the prefill kernel on piece i and the device->host copy of the output of
+    piece i-1 run at the same time (PCIe is full duplex).  K, V and the role codes of all pieces stay on the device
+    afterwards (``self.k``, ``self.v``, ``self.roles``) because the eviction that follows a prefill needs them.
+    Device buffers are allocated once and reused by later calls of the same shape."""
+
+    def __init__(self, B: int, Hq: int, Hkv: int, N: int, D: int, chunk_size: int, sliding_window: int,
+                 device: torch.device, n_buffers: int = 3):
+        self.shape = (B, Hq, Hkv, N, D)
+        self.C, self.SW, self.device = chunk_size, sliding_window, device
+        nrep = Hq // Hkv
+        self.k = torch.empty(B, Hkv, N, D, dtype=torch.bfloat16, device=device)
+        self.v = torch.empty_like(self.k)
+        self.roles = torch.empty(B, Hkv, -(-N // chunk_size), dtype=torch.uint8, device=device)
+        self.q_buf = [torch.empty(1, nrep, N, D, dtype=torch.bfloat16, device=device) for _ in range(n_buffers)]
+        self.o_buf = [torch.empty(1, nrep, N, D, dtype=torch.bfloat16, device=device) for _ in range(n_buffers)]
+        self.s_in, self.s_out = torch.cuda.Stream(device), torch.cuda.Stream(device)
+        self.kept = torch.zeros(B, Hkv, dtype=torch.int64, device=device)
+
+    def run(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, roles: torch.Tensor, out: torch.Tensor,
+            sm_scale: float | None = None) -> torch.Tensor:
+        B, Hq, Hkv, N, D = self.shape
+        nrep, nb = Hq // Hkv, len(self.q_buf)
+        main = torch.cuda.current_stream(self.device)
+        self.s_in.wait_stream(main)
+        self.s_out.wait_stream(main)
+        with torch.cuda.stream(self.s_in):
+            self.roles.copy_(roles, non_blocking=True)
+        copied = [None] * (B * Hkv)
+        computed = [None] * (B * Hkv)
+        drained = [None] * (B * Hkv)
+        for i in range(B * Hkv):
+            b, h = divmod(i, Hkv)
+            slot = i % nb
+            with torch.cuda.stream(self.s_in):
+                if i >= nb:
+                    self.s_in.wait_event(computed[i - nb])            # the kernel that read this q buffer is done
+                self.q_buf[slot].copy_(q[b:b + 1, h * nrep:(h + 1) * nrep], non_blocking=True)
+                self.k[b, h].copy_(k[b, h], non_blocking=True)
+                self.v[b, h].copy_(v[b, h], non_blocking=True)
+                copied[i] = torch.cuda.Event()
+                copied[i].record(self.s_in)
+            main.wait_event(copied[i])
+            if i >= nb:
+                main.wait_event(drained[i - nb])                      # the output buffer has been copied out
+            o = prefill_attention(self.q_buf[slot], self.k[b:b + 1, h:h + 1], self.v[b:b + 1, h:h + 1], self.roles[b:b + 1, h:h + 1],
+                                  self.C, self.SW, sm_scale, kept_tiles=self.kept[b:b + 1, h:h + 1], out=self.o_buf[slot])
+            computed[i] = torch.cuda.Event()
+            computed[i].record(main)
+            with torch.cuda.stream(self.s_out):
+                self.s_out.wait_event(computed[i])
+                out[b:b + 1, h * nrep:(h + 1) * nrep].copy_(o, non_blocking=True)
+                drained[i] = torch.cuda.Event()
+                drained[i].record(self.s_out)
+        main.wait_stream(self.s_out)
+        return out
 
 
 def dense_role_mask(roles: torch.Tensor, chunk_size: int, sliding_window: int, n: int) -> torch.Tensor:

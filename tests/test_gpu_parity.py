@@ -572,3 +572,21 @@ def test_decode_configuration_batch64_ragged():
                                        lc._buf_v[b:b + 1, h:h + 1, :n].float().cpu().numpy(), mask)
             assert_close_attn(o[b:b + 1, h * 4:h * 4 + 4], ref, f'step {step} pair ({b},{h})')
         lc.post_update(1)
+
+
+def test_host_pipeline_equals_device_prefill():
+    """The pipelined host-buffer entry (copy-in / kernel / copy-out per (batch, kv-head) piece on three streams) returns
+    what one device-resident call returns, twice in a row with the buffers reused."""
+    from neuralattentionsearch_b200 import HostPrefillPipeline, check_status, prefill_attention
+    B, Hq, Hkv, N, D, C, SW = 2, 8, 4, 1024, 128, 64, 256
+    pipe = HostPrefillPipeline(B, Hq, Hkv, N, D, C, SW, dev())
+    for seed in (1, 2):
+        roles = torch.from_numpy(orc.make_roles(B, Hkv, N // C, 0.1, 0.3, seed=seed)).pin_memory()
+        q, k, v = (t.bfloat16().pin_memory() for t in inputs(B, Hq, Hkv, N, D, seed=seed, sigma=0.5))
+        out = torch.empty_like(q).pin_memory()
+        pipe.run(q, k, v, roles, out)
+        torch.cuda.synchronize()
+        check_status(dev())
+        ref = prefill_attention(q.to(dev()), k.to(dev()), v.to(dev()), roles.to(dev()), C, SW)
+        assert torch.equal(out, ref.cpu())
+        assert torch.equal(pipe.k.cpu(), k) and torch.equal(pipe.roles.cpu(), roles)
