@@ -1,10 +1,12 @@
 // Role-masked chunked flash-attention prefill for sm_100a: TMA-fed tcgen05.mma with TMEM accumulators.
 //
-// One CTA = one 128-row query tile x one kv-head x up to two query heads of that kv-head's group.  The two heads
+// A work item = one 128-row query tile x one kv-head x up to two query heads of that kv-head's group.  The two heads
 // share every K/V tile that is loaded and keep the tensor pipe busy in turns: while the softmax warps of one head
-// work on S = Q.K^T in TMEM, the tensor core runs the other head's MMAs.
+// work on S = Q.K^T in TMEM, the tensor core runs the other head's MMAs.  The kernel is persistent: one CTA per SM
+// takes items from a global counter (heaviest query tiles first).
 //
-//   warp 0      TMA producer: Q (once), then K and V of every kept KV tile through 2-stage rings
+//   warp 0      TMA producer: Q of an item, then K and V of every kept KV tile through 2-stage rings
+//   warp 3      scheduler: fetches the next item and builds its kept-tile list while the current item runs
 //   warps 1,2   MMA issuers of head slot 0 / 1 (one elected lane each): S_h = Q_h.K^T (SS), O_h += P_h.V (TS, P from TMEM)
 //   warps 4-7   softmax of head slot 0: one thread per query row, S read with tcgen05.ld, online softmax in
 //   warps 8-11  softmax of head slot 1  registers, P written back over S as packed bf16 with tcgen05.st
@@ -24,10 +26,18 @@ namespace nats {
 constexpr int kPrefillThreads = 384;
 constexpr int kStages = 2;
 constexpr uint32_t kBoxBytes = 128 * 64 * 2;            // one TMA box: 128 rows x 64 bf16, 128-byte swizzled
+#ifndef NATS_RELAX_NS
+#define NATS_RELAX_NS 200
+#endif
+constexpr int kRelaxNs = NATS_RELAX_NS;
+#ifndef NATS_RELAX_PROD_NS
+#define NATS_RELAX_PROD_NS 0
+#endif
+constexpr int kRelaxProdNs = NATS_RELAX_PROD_NS;
 constexpr float kRescaleThreshold = 8.0f;               // log2 units: O is rescaled only when the row max grows by more
 constexpr unsigned long long kWaitLimitNs = 400ull * 1000ull * 1000ull;
 
-enum : int { kErrQ = 1, kErrKFull, kErrVFull, kErrKEmpty, kErrVEmpty, kErrSFull, kErrPFull, kErrOFull, kErrTurn };
+enum : int { kErrQ = 1, kErrKFull, kErrVFull, kErrKEmpty, kErrVEmpty, kErrSFull, kErrPFull, kErrOFull, kErrTurn, kErrList, kErrOEmpty };
 
 struct PrefillParams {
     __nv_bfloat16* o;                 // [B,Hq,N,D]
@@ -35,21 +45,11 @@ struct PrefillParams {
     const int32_t* tile_max;          // [B,Hkv,Nt]
     const int32_t* tile_min;
     int32_t* status;
+    int32_t* work_counter;            // next work item; zero at launch
+    int total_items;                  // B * Hkv * n_groups * Nt
     int Hq, Hkv, N, C, Nc, Nt, nrep, n_groups;   // n_groups = ceil(nrep / 2)
     float scale_log2;
 };
-
-#ifdef NATS_TRACE
-// Development aid (never compiled into the shipped library): cycle stamps of the first CTA's pipeline stages.
-__device__ long long g_trace[2 * 64 * 8];
-#define NATS_STAMP(role, jt, slot)                                                                      \
-    do {                                                                                                \
-        if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0 && (jt) < 64)           \
-            g_trace[((role) * 64 + (jt)) * 8 + (slot)] = clock64();                                     \
-    } while (0)
-#else
-#define NATS_STAMP(role, jt, slot) do {} while (0)
-#endif
 
 // ---- PTX wrappers -------------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -79,11 +79,15 @@ __device__ __forceinline__ unsigned long long global_ns() {
 }
 // Bounded wait.  Returns false when the wait was given up (by this thread or, earlier, by another one of the CTA).
 // With abort_flag == nullptr only the time limit ends the wait (used to drain copies after the CTA has given up).
+// RELAX > 0: sleep that many nanoseconds between polls (roles that run ahead of the critical path and should not take
+// issue slots from the softmax warps of their scheduler).
+template <int RELAX = 0>
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int32_t* status, int code) {
     if (mbar_try_wait(bar, parity)) return true;
     const unsigned long long t0 = global_ns();
 #pragma unroll 1
     for (uint32_t it = 0;; ++it) {
+        if (RELAX > 0) __nanosleep(RELAX);
         if (mbar_try_wait(bar, parity)) return true;
         if ((it & 63u) == 63u) {
             if (abort_flag != nullptr && *abort_flag) return false;
@@ -205,20 +209,38 @@ __host__ __device__ constexpr uint32_t instr_desc(int n, bool b_mn_major) {
 }
 
 // ---- shared memory --------------------------------------------------------------------------------
+struct ItemHeader {
+    int valid;      // 0: no more work
+    int t;          // query tile
+    int b, bh;      // batch index, b * Hkv + kv-head
+    int head0;      // query head of slot 0
+    int nslots;     // 1 or 2 query heads in this item
+    int n_kept;     // kept KV tiles
+    int pad;
+};
+
 template <int D>
 struct __align__(1024) PrefillSmem {
     uint8_t q[2][128 * D * 2];             // one tile per head slot; D/64 boxes of 16 KB each
     uint8_t k[kStages][128 * D * 2];
     uint8_t v[kStages][128 * D * 2];
-    uint16_t list[kMaxTiles];              // kept KV tiles of this query tile, ascending; bit 15 = needs element masking
-    int seg_count[kMaxTiles / 32];
-    unsigned long long bar_q, bar_k_full[kStages], bar_k_empty[kStages], bar_v_full[kStages], bar_v_empty[kStages];
-    unsigned long long bar_s_full[2], bar_p_full[2], bar_o_full[2], bar_turn[2];
+    uint16_t list[2][kMaxTiles];           // kept KV tiles of an item, ascending; bit 15 = needs element masking (double buffered)
+    ItemHeader item[2];
+    unsigned long long bar_q_full, bar_q_empty;
+    unsigned long long bar_k_full[kStages], bar_k_empty[kStages], bar_v_full[kStages], bar_v_empty[kStages];
+    unsigned long long bar_s_full[2], bar_p_full[2], bar_o_full[2], bar_o_empty[2], bar_turn[2];
+    unsigned long long bar_list_full[2], bar_list_empty[2];
     uint32_t tmem_base;
-    int n_kept;
     int abort_flag;
 };
 
+constexpr int kListConsumers = 1 + 2 + 8;     // producer, two issuers, one lane of each of the eight softmax warps
+
+// Persistent kernel: every CTA takes work items (query tile x kv-head x head pair) from a global counter until none is
+// left.  Per-item set-up (kept-tile list, Q load) and tear-down (O -> global) overlap the main loops of the neighbouring
+// items: warp 3 prepares the list of the next item while the current one runs, the producer streams the next item's K/V
+// through the same rings without a bubble, Q of the next item is loaded as soon as the last Q.K^T of the current one
+// has completed, and a head's epilogue only delays that head's own chain.
 template <int D>
 __global__ void __launch_bounds__(kPrefillThreads, 1)
 prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
@@ -231,34 +253,30 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     constexpr uint32_t IDESC_PV = instr_desc(D, true);
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int t = p.Nt - 1 - (int)blockIdx.x;          // heavy (late) query tiles are scheduled first
-    const int grp = blockIdx.y % p.n_groups, hkv = blockIdx.y / p.n_groups, b = blockIdx.z;
-    const int bh = b * p.Hkv + hkv;
-    const int head0 = hkv * p.nrep + grp * 2;          // query head of slot 0
-    const int nslots = min(2, p.nrep - grp * 2);
-    const int q_lo = t * kTile;
-    const int q_hi = min(q_lo + kTile, p.N) - 1;
     volatile int* abort_flag = &sm.abort_flag;
 
-    if (warp == 1) NATS_STAMP(1, 60, 7);
     if (tid == 0) sm.abort_flag = (*reinterpret_cast<volatile int32_t*>(p.status) != 0);
     __syncthreads();
     if (sm.abort_flag) return;                         // an earlier CTA gave up: do not start (uniform for the CTA)
 
-    // ---- set-up: barriers, TMEM, Q load ----
+    // ---- set-up: barriers, TMEM ----
     if (tid == 0) {
-        mbar_init(smem_u32(&sm.bar_q), 1);
+        mbar_init(smem_u32(&sm.bar_q_full), 1);
+        mbar_init(smem_u32(&sm.bar_q_empty), 2);                   // one commit per MMA issuer
         for (int s = 0; s < kStages; ++s) {
             mbar_init(smem_u32(&sm.bar_k_full[s]), 1);
-            mbar_init(smem_u32(&sm.bar_k_empty[s]), nslots);      // one commit per MMA issuer
+            mbar_init(smem_u32(&sm.bar_k_empty[s]), 2);
             mbar_init(smem_u32(&sm.bar_v_full[s]), 1);
-            mbar_init(smem_u32(&sm.bar_v_empty[s]), nslots);
+            mbar_init(smem_u32(&sm.bar_v_empty[s]), 2);
         }
         for (int h = 0; h < 2; ++h) {
             mbar_init(smem_u32(&sm.bar_s_full[h]), 1);
             mbar_init(smem_u32(&sm.bar_p_full[h]), 128);
             mbar_init(smem_u32(&sm.bar_o_full[h]), 1);
+            mbar_init(smem_u32(&sm.bar_o_empty[h]), 128);
             mbar_init(smem_u32(&sm.bar_turn[h]), 1);
+            mbar_init(smem_u32(&sm.bar_list_full[h]), 1);
+            mbar_init(smem_u32(&sm.bar_list_empty[h]), kListConsumers);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         prefetch_tmap(&map_q);
@@ -271,99 +289,118 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         tc_fence_before();
     }
     __syncthreads();
-    if (tid == 0) {
-        mbar_expect_tx(smem_u32(&sm.bar_q), nslots * TILE_BYTES);
-        for (int h = 0; h < nslots; ++h)
-            for (int x = 0; x < NBOX; ++x)
-                tma_load_3d(smem_u32(&sm.q[h][x * kBoxBytes]), &map_q, smem_u32(&sm.bar_q), x * 64, q_lo, b * p.Hq + head0 + h);
-    }
-
-    // ---- kept-tile list: ordered compaction of the tiles 0..t that hold a visible entry ----
-    {
-        const int32_t* tmax = p.tile_max + (size_t)bh * p.Nt;
-        const int32_t* tmin = p.tile_min + (size_t)bh * p.Nt;
-        const int nseg = (t + 32) / 32;                // tiles 0..t in segments of 32
-        constexpr int NW = kPrefillThreads / 32;
-        for (int s = warp; s < nseg; s += NW) {
-            const int kt = s * 32 + lane;
-            const bool keep = kt <= t && tmax[kt] >= q_lo;
-            const unsigned m = __ballot_sync(0xffffffffu, keep);
-            if (lane == 0) sm.seg_count[s] = __popc(m);
-        }
-        __syncthreads();
-        if (warp == 0) {                               // exclusive scan of the segment counts
-            int carry = 0;
-            for (int s0 = 0; s0 < nseg; s0 += 32) {
-                const int s = s0 + lane;
-                const int c = s < nseg ? sm.seg_count[s] : 0;
-                const int inc = warp_incl_scan(c, lane);
-                if (s < nseg) sm.seg_count[s] = carry + inc - c;
-                carry += __shfl_sync(0xffffffffu, inc, 31);
-            }
-            if (lane == 0) sm.n_kept = carry;
-        }
-        __syncthreads();
-        for (int s = warp; s < nseg; s += NW) {
-            const int kt = s * 32 + lane;
-            const bool keep = kt <= t && tmax[kt] >= q_lo;
-            const unsigned m = __ballot_sync(0xffffffffu, keep);
-            if (keep) {
-                const bool partial = kt == t || tmin[kt] < q_hi;
-                sm.list[sm.seg_count[s] + __popc(m & ((1u << lane) - 1u))] = (uint16_t)(kt | (partial ? 0x8000 : 0));
-            }
-        }
-        __syncthreads();
-    }
-    const int n_kept = sm.n_kept;
-    if (warp == 1) NATS_STAMP(1, 61, 7);
     tc_fence_after();
     const uint32_t tmem = sm.tmem_base;
 
     // Register budget: the softmax warpgroups hold a whole score row per thread (setmaxnreg.inc at the top of their
-    // branch), the producer / issuer warpgroup needs little and gives registers back (setmaxnreg.dec in its branches).
+    // branch), the producer / issuer / scheduler warpgroup needs little and gives registers back.
     if (warp < 4) asm volatile("setmaxnreg.dec.sync.aligned.u32 48;");      // one site for the whole warpgroup
-    if (warp == 0) {
-        // =============================== TMA producer ===============================
-        int issued_k = 0, issued_v = 0;
+
+    if (warp == 3) {
+        // =============================== scheduler: next work item and its kept-tile list ===============================
+        const int per_z = p.Nt * p.Hkv * p.n_groups;
         bool ok = true;
-        for (int jt = 0; jt < n_kept && ok; ++jt) {
-            const int kt = sm.list[jt] & 0x7fff;
-            const int s = jt % kStages;
-            const uint32_t ph = (jt / kStages) & 1;
-            if (jt >= kStages) ok = mbar_wait(smem_u32(&sm.bar_k_empty[s]), ph ^ 1, abort_flag, p.status, kErrKEmpty);
+        for (int ic = 0; ok; ++ic) {
+            const int slot = ic & 1, use = ic >> 1;
+            if (use > 0) ok = mbar_wait<kRelaxNs>(smem_u32(&sm.bar_list_empty[slot]), (use - 1) & 1, abort_flag, p.status, kErrList);
             if (!ok) break;
-            if (lane == 0) {
-                mbar_expect_tx(smem_u32(&sm.bar_k_full[s]), TILE_BYTES);
-                for (int x = 0; x < NBOX; ++x)
-                    tma_load_3d(smem_u32(&sm.k[s][x * kBoxBytes]), &map_k, smem_u32(&sm.bar_k_full[s]), x * 64, kt * kTile, bh);
+            int w = 0;
+            if (lane == 0) w = atomicAdd(p.work_counter, 1);
+            w = __shfl_sync(0xffffffffu, w, 0);
+            const bool have = w < p.total_items;
+            int n_kept = 0;
+            if (have) {
+                const int z = w / per_z, rem = w - z * per_z;
+                const int y = rem / p.Nt, x = rem - y * p.Nt;
+                const int t = p.Nt - 1 - x;                        // heavy (late) query tiles first
+                const int grp = y % p.n_groups, hkv = y / p.n_groups;
+                const int bh = z * p.Hkv + hkv;
+                const int q_lo = t * kTile, q_hi = min(q_lo + kTile, p.N) - 1;
+                const int32_t* tmax = p.tile_max + (size_t)bh * p.Nt;
+                const int32_t* tmin = p.tile_min + (size_t)bh * p.Nt;
+                for (int s0 = 0; s0 <= t; s0 += 32) {              // ordered compaction of the tiles 0..t with a visible entry
+                    const int kt = s0 + lane;
+                    const bool keep = kt <= t && tmax[kt] >= q_lo;
+                    const unsigned m = __ballot_sync(0xffffffffu, keep);
+                    if (keep) {
+                        const bool partial = kt == t || tmin[kt] < q_hi;
+                        sm.list[slot][n_kept + __popc(m & ((1u << lane) - 1u))] = (uint16_t)(kt | (partial ? 0x8000 : 0));
+                    }
+                    n_kept += __popc(m);
+                }
+                if (lane == 0) {
+                    ItemHeader hd;
+                    hd.valid = 1; hd.t = t; hd.b = z; hd.bh = bh; hd.head0 = hkv * p.nrep + grp * 2;
+                    hd.nslots = min(2, p.nrep - grp * 2); hd.n_kept = n_kept; hd.pad = 0;
+                    sm.item[slot] = hd;
+                }
+            } else if (lane == 0) {
+                sm.item[slot].valid = 0;
             }
-            ++issued_k;
-            if (jt >= kStages) ok = mbar_wait(smem_u32(&sm.bar_v_empty[s]), ph ^ 1, abort_flag, p.status, kErrVEmpty);
-            if (!ok) break;
-            if (lane == 0) {
-                mbar_expect_tx(smem_u32(&sm.bar_v_full[s]), TILE_BYTES);
-                for (int x = 0; x < NBOX; ++x)
-                    tma_load_3d(smem_u32(&sm.v[s][x * kBoxBytes]), &map_v, smem_u32(&sm.bar_v_full[s]), x * 64, kt * kTile, bh);
-            }
-            ++issued_v;
             __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&sm.bar_list_full[slot]));
+            if (!have) break;
+        }
+    } else if (warp == 0) {
+        // =============================== TMA producer ===============================
+        uint32_t g = 0;                                 // tiles pushed through the K / V rings so far (all items)
+        uint32_t issued_k = 0, issued_v = 0;
+        bool ok = true;
+        for (int ic = 0; ok; ++ic) {
+            const int slot = ic & 1;
+            ok = mbar_wait(smem_u32(&sm.bar_list_full[slot]), (ic >> 1) & 1, abort_flag, p.status, kErrList);
+            if (!ok) break;
+            const ItemHeader hd = sm.item[slot];
+            if (!hd.valid) break;
+            // Q of this item may overwrite the previous one once both issuers have committed their last Q.K^T
+            if (ic > 0) ok = mbar_wait(smem_u32(&sm.bar_q_empty), (ic - 1) & 1, abort_flag, p.status, kErrQ);
+            if (!ok) break;
+            if (lane == 0) {
+                mbar_expect_tx(smem_u32(&sm.bar_q_full), hd.nslots * TILE_BYTES);
+                for (int h = 0; h < hd.nslots; ++h)
+                    for (int x = 0; x < NBOX; ++x)
+                        tma_load_3d(smem_u32(&sm.q[h][x * kBoxBytes]), &map_q, smem_u32(&sm.bar_q_full), x * 64, hd.t * kTile,
+                                    hd.b * p.Hq + hd.head0 + h);
+            }
+            for (int jt = 0; jt < hd.n_kept && ok; ++jt, ++g) {
+                const int kt = sm.list[slot][jt] & 0x7fff;
+                const int s = g % kStages;
+                const uint32_t ph = (g / kStages) & 1;
+                if (g >= kStages) ok = mbar_wait<kRelaxProdNs>(smem_u32(&sm.bar_k_empty[s]), ph ^ 1, abort_flag, p.status, kErrKEmpty);
+                if (!ok) break;
+                if (lane == 0) {
+                    mbar_expect_tx(smem_u32(&sm.bar_k_full[s]), TILE_BYTES);
+                    for (int x = 0; x < NBOX; ++x)
+                        tma_load_3d(smem_u32(&sm.k[s][x * kBoxBytes]), &map_k, smem_u32(&sm.bar_k_full[s]), x * 64, kt * kTile, hd.bh);
+                }
+                ++issued_k;
+                if (g >= kStages) ok = mbar_wait<kRelaxProdNs>(smem_u32(&sm.bar_v_empty[s]), ph ^ 1, abort_flag, p.status, kErrVEmpty);
+                if (!ok) break;
+                if (lane == 0) {
+                    mbar_expect_tx(smem_u32(&sm.bar_v_full[s]), TILE_BYTES);
+                    for (int x = 0; x < NBOX; ++x)
+                        tma_load_3d(smem_u32(&sm.v[s][x * kBoxBytes]), &map_v, smem_u32(&sm.bar_v_full[s]), x * 64, kt * kTile, hd.bh);
+                }
+                ++issued_v;
+                __syncwarp();
+            }
+            if (ok && lane == 0) mbar_arrive(smem_u32(&sm.bar_list_empty[slot]));
         }
         if (!ok) {
             // given up: let copies that are still in flight land before the shared memory is released
-            for (int jt = max(0, issued_k - kStages); jt < issued_k; ++jt)
-                mbar_wait(smem_u32(&sm.bar_k_full[jt % kStages]), (jt / kStages) & 1, nullptr, p.status, kErrKFull);
-            for (int jt = max(0, issued_v - kStages); jt < issued_v; ++jt)
-                mbar_wait(smem_u32(&sm.bar_v_full[jt % kStages]), (jt / kStages) & 1, nullptr, p.status, kErrVFull);
+            for (uint32_t x = issued_k > kStages ? issued_k - kStages : 0; x < issued_k; ++x)
+                mbar_wait(smem_u32(&sm.bar_k_full[x % kStages]), (x / kStages) & 1, nullptr, p.status, kErrKFull);
+            for (uint32_t x = issued_v > kStages ? issued_v - kStages : 0; x < issued_v; ++x)
+                mbar_wait(smem_u32(&sm.bar_v_full[x % kStages]), (x / kStages) & 1, nullptr, p.status, kErrVFull);
         }
-    } else if (warp == 1 || (warp == 2 && nslots == 2)) {
+    } else if (warp == 1 || warp == 2) {
         // =============================== MMA issuers: warp 1 for head slot 0, warp 2 for head slot 1 ===============================
         // Each issuer owns the chain of its head: O_h += P_h.V for tile j, then S_h = Q_h.K^T for tile j+1 (which may only
-        // overwrite S_h once the MMA reading P_h from it has been issued).  While one issuer waits for its softmax
-        // warps, the tensor core runs the other issuer's MMAs.  K/V stages are released when both issuers have committed.
+        // overwrite S_h once the MMA reading P_h from it has been issued).  The two issuers take turns (a token passed
+        // through bar_turn): the heads stay half a period apart, so one head's exponentials overlap the other head's MMAs
+        // instead of both competing for the same unit at once.  K/V stages and Q are released when both issuers have
+        // committed; an issuer whose head slot is empty in an item (odd group size) only keeps the barrier counts going.
         const int h = warp - 1;
-        const bool two = nslots == 2;
-        bool ok = mbar_wait(smem_u32(&sm.bar_q), 0, abort_flag, p.status, kErrQ);
-        // descriptors of the tiles: only the start-address field (low word, in 16-byte units) moves between MMAs
         constexpr uint32_t TILE16 = TILE_BYTES >> 4;
         const uint64_t q_desc = smem_desc(smem_u32(&sm.q[0][0]), 16, 1024) + (uint64_t)(h * TILE16);
         const uint64_t k_desc0 = smem_desc(smem_u32(&sm.k[0][0]), 16, 1024);
@@ -386,190 +423,225 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
 #pragma unroll
             for (int ks = 1; ks < 8; ++ks) mma_ts(dO, dS + ks * 8, vd + (uint64_t)(ks * (2048 >> 4)), IDESC_PV, 1u);
         };
-        if (ok && n_kept > 0) {
-            ok = mbar_wait(smem_u32(&sm.bar_k_full[0]), 0, abort_flag, p.status, kErrKFull);
-            // The two issuers take turns (a token passed through bar_turn): the heads stay half a period apart, so one
-            // head's exponentials overlap the other head's MMAs instead of both competing for the same unit at once.
-            if (ok && two && h == 1) ok = mbar_wait(smem_u32(&sm.bar_turn[1]), 0, abort_flag, p.status, kErrTurn);
-            if (ok) {
-                tc_fence_after();
-                if (lane == 0) {
-                    issue_qk(0);
-                    tc_commit(smem_u32(&sm.bar_s_full[h]));
-                    tc_commit(smem_u32(&sm.bar_k_empty[0]));
-                    if (two) mbar_arrive(smem_u32(&sm.bar_turn[1 - h]));
-                }
-                __syncwarp();
-            }
-        }
-        for (int jt = 0; jt < n_kept && ok; ++jt) {
-            const int s = jt % kStages;
-            const uint32_t ph = (jt / kStages) & 1;
-            const bool has_next = jt + 1 < n_kept;
-            const int sn = (jt + 1) % kStages;
-            const uint32_t phn = ((jt + 1) / kStages) & 1;
-            if (warp == 1) NATS_STAMP(1, jt, 0);
-            ok = mbar_wait(smem_u32(&sm.bar_v_full[s]), ph, abort_flag, p.status, kErrVFull);
-            if (ok && has_next) ok = mbar_wait(smem_u32(&sm.bar_k_full[sn]), phn, abort_flag, p.status, kErrKFull);
-            if (ok) ok = mbar_wait(smem_u32(&sm.bar_p_full[h]), jt & 1, abort_flag, p.status, kErrPFull);
-            // turn n = jt + 1 of this issuer: issuer 0 follows issuer 1's turn n - 1, issuer 1 follows issuer 0's turn n
-            if (ok && two) ok = mbar_wait(smem_u32(&sm.bar_turn[h]), (h == 0 ? jt : jt + 1) & 1, abort_flag, p.status, kErrTurn);
+        uint32_t g = 0;          // tiles through the K / V rings (all items, both issuers count alike)
+        uint32_t gh = 0;         // tiles of this head (items in which its slot is used)
+        uint32_t na = 0;         // items in which this head's slot was used
+        uint32_t turns = 0;      // turns taken in two-head items
+        bool ok = true;
+        auto take_turn = [&]() {
+            // issuer 0 follows issuer 1's previous turn, issuer 1 follows issuer 0's turn of the same number
+            if (h == 0) return turns == 0 ? true : mbar_wait(smem_u32(&sm.bar_turn[0]), (turns - 1) & 1, abort_flag, p.status, kErrTurn);
+            return mbar_wait(smem_u32(&sm.bar_turn[1]), turns & 1, abort_flag, p.status, kErrTurn);
+        };
+        for (int ic = 0; ok; ++ic) {
+            const int slot = ic & 1;
+            ok = mbar_wait(smem_u32(&sm.bar_list_full[slot]), (ic >> 1) & 1, abort_flag, p.status, kErrList);
             if (!ok) break;
-            if (warp == 1) NATS_STAMP(1, jt, 1);
+            const ItemHeader hd = sm.item[slot];
+            if (!hd.valid) break;
+            const int n = hd.n_kept;
+            const bool active = h < hd.nslots, two = hd.nslots == 2;
+            if (active) ok = mbar_wait(smem_u32(&sm.bar_q_full), ic & 1, abort_flag, p.status, kErrQ);
+            // ---- first tile: S_h = Q_h.K^T ----
+            if (ok) ok = mbar_wait(smem_u32(&sm.bar_k_full[g % kStages]), (g / kStages) & 1, abort_flag, p.status, kErrKFull);
+            if (ok && active && two) ok = take_turn();
+            if (!ok) break;
             tc_fence_after();
             if (lane == 0) {
-                issue_pv(s, jt == 0);
-                if (!has_next) tc_commit(smem_u32(&sm.bar_o_full[h]));
-                tc_commit(smem_u32(&sm.bar_v_empty[s]));
-                if (has_next) {
-                    issue_qk(sn);
+                if (active) {
+                    issue_qk(g % kStages);
                     tc_commit(smem_u32(&sm.bar_s_full[h]));
-                    tc_commit(smem_u32(&sm.bar_k_empty[sn]));
                 }
-                if (two) mbar_arrive(smem_u32(&sm.bar_turn[1 - h]));
+                tc_commit(smem_u32(&sm.bar_k_empty[g % kStages]));
+                if (n == 1) tc_commit(smem_u32(&sm.bar_q_empty));
+                if (active && two) mbar_arrive(smem_u32(&sm.bar_turn[1 - h]));
             }
-            if (warp == 1) NATS_STAMP(1, jt, 2);
+            if (active && two) ++turns;
             __syncwarp();
+            // ---- tiles ----
+            for (int jt = 0; jt < n && ok; ++jt, ++g) {
+                const int s = g % kStages;
+                const uint32_t ph = (g / kStages) & 1;
+                const bool has_next = jt + 1 < n;
+                const int sn = (g + 1) % kStages;
+                const uint32_t phn = ((g + 1) / kStages) & 1;
+                ok = mbar_wait(smem_u32(&sm.bar_v_full[s]), ph, abort_flag, p.status, kErrVFull);
+                if (ok && has_next) ok = mbar_wait(smem_u32(&sm.bar_k_full[sn]), phn, abort_flag, p.status, kErrKFull);
+                if (ok && active) ok = mbar_wait(smem_u32(&sm.bar_p_full[h]), gh & 1, abort_flag, p.status, kErrPFull);
+                // the first P.V of an item overwrites O_h: the previous item's epilogue must have read it
+                if (ok && active && jt == 0 && na > 0) ok = mbar_wait(smem_u32(&sm.bar_o_empty[h]), (na - 1) & 1, abort_flag, p.status, kErrOEmpty);
+                if (ok && active && two) ok = take_turn();
+                if (!ok) break;
+                tc_fence_after();
+                if (lane == 0) {
+                    if (active) {
+                        issue_pv(s, jt == 0);
+                        if (!has_next) tc_commit(smem_u32(&sm.bar_o_full[h]));
+                    }
+                    tc_commit(smem_u32(&sm.bar_v_empty[s]));
+                    if (has_next) {
+                        if (active) {
+                            issue_qk(sn);
+                            tc_commit(smem_u32(&sm.bar_s_full[h]));
+                        }
+                        tc_commit(smem_u32(&sm.bar_k_empty[sn]));
+                        if (jt + 2 == n) tc_commit(smem_u32(&sm.bar_q_empty));      // that was the last Q.K^T of the item
+                    }
+                    if (active && two) mbar_arrive(smem_u32(&sm.bar_turn[1 - h]));
+                }
+                if (active && two) ++turns;
+                if (active) ++gh;
+                __syncwarp();
+            }
+            if (active) ++na;
+            if (ok && lane == 0) mbar_arrive(smem_u32(&sm.bar_list_empty[slot]));
         }
-    } else if (warp >= 4 && warp < 4 + 4 * nslots) {
+    } else if (warp >= 4) {
         // =============================== softmax + epilogue ===============================
         asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
         const int h = (warp - 4) / 4;                    // head slot
         const int row = (warp & 3) * 32 + lane;          // query row inside the tile == TMEM lane
-        const int qi = q_lo + row;                       // query token index
         const uint32_t lane_addr = ((uint32_t)((warp & 3) * 32)) << 16;
         const uint32_t tS = tmem + lane_addr + h * 128;
         const uint32_t tO = tmem + lane_addr + 256 + h * 128;
-        const int32_t* lim = p.lim + (size_t)bh * p.Nc;
         const float scale = p.scale_log2;
-        float m_ref = -INFINITY, l_sum = 0.f;
+        uint32_t gh = 0, na = 0;                         // tiles / items of this head so far
         bool ok = true;
-        for (int jt = 0; jt < n_kept; ++jt) {
-            const int entry = sm.list[jt];
-            const int kt = entry & 0x7fff;
-            const bool partial = (entry & 0x8000) != 0;
-            // visibility bits of this row for the 128 columns of a tile that is not fully visible
-            uint32_t bits[4] = {0xffffffffu, 0xffffffffu, 0xffffffffu, 0xffffffffu};
-            if (partial) {
-                // columns this row may see: the causal prefix (and nothing past N), minus every chunk whose row limit is below it
-                const int k0 = kt * kTile;
-                const int nvis = max(0, min(min(qi - k0 + 1, p.N - k0), kTile));
-#pragma unroll
-                for (int w = 0; w < 4; ++w) bits[w] = range_mask(0, nvis, w);
-                const int c_first = k0 / p.C, c_last = min((k0 + kTile - 1) / p.C, p.Nc - 1);
-#pragma unroll 1
-                for (int cc = c_first; cc <= c_last; ++cc) {
-                    if (qi > lim[cc]) {
-                        const int lo = max(cc * p.C - k0, 0), hi = min((cc + 1) * p.C - k0, kTile);
-#pragma unroll
-                        for (int w = 0; w < 4; ++w) bits[w] &= ~range_mask(lo, hi, w);
-                    }
-                }
-            }
-            if (warp == 4) NATS_STAMP(0, jt, 0);
-            ok = mbar_wait(smem_u32(&sm.bar_s_full[h]), jt & 1, abort_flag, p.status, kErrSFull);
+        for (int ic = 0; ok; ++ic) {
+            const int slot = ic & 1;
+            ok = mbar_wait(smem_u32(&sm.bar_list_full[slot]), (ic >> 1) & 1, abort_flag, p.status, kErrList);
             if (!ok) break;
-            tc_fence_after();
-            if (warp == 4) NATS_STAMP(0, jt, 1);
-            // the whole score row of this thread in registers: four loads in flight, one wait
-            uint32_t sreg[128];
-            tmem_ld32(tS + 0, *reinterpret_cast<uint32_t(*)[32]>(&sreg[0]));
-            tmem_ld32(tS + 32, *reinterpret_cast<uint32_t(*)[32]>(&sreg[32]));
-            tmem_ld32(tS + 64, *reinterpret_cast<uint32_t(*)[32]>(&sreg[64]));
-            tmem_ld32(tS + 96, *reinterpret_cast<uint32_t(*)[32]>(&sreg[96]));
-            tc_wait_ld();
-            if (partial) {
+            const ItemHeader hd = sm.item[slot];
+            if (!hd.valid) break;
+            if (h < hd.nslots) {
+                const int n_kept = hd.n_kept;
+                const int q_lo = hd.t * kTile;
+                const int qi = q_lo + row;                       // query token index
+                const int32_t* lim = p.lim + (size_t)hd.bh * p.Nc;
+                float m_ref = -INFINITY, l_sum = 0.f;
+                for (int jt = 0; jt < n_kept; ++jt, ++gh) {
+                    const int entry = sm.list[slot][jt];
+                    const int kt = entry & 0x7fff;
+                    const bool partial = (entry & 0x8000) != 0;
+                    // visibility bits of this row for the 128 columns of a tile that is not fully visible
+                    uint32_t bits[4] = {0xffffffffu, 0xffffffffu, 0xffffffffu, 0xffffffffu};
+                    if (partial) {
+                        // columns this row may see: the causal prefix (and nothing past N), minus every chunk whose row limit is below it
+                        const int k0 = kt * kTile;
+                        const int nvis = max(0, min(min(qi - k0 + 1, p.N - k0), kTile));
 #pragma unroll
-                for (int i = 0; i < 128; ++i)
-                    if (!((bits[i >> 5] >> (i & 31)) & 1u)) sreg[i] = 0xff800000u;      // -inf: exp2 gives exactly 0
-            }
-            float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
-#pragma unroll
-            for (int i = 0; i < 128; i += 4) {
-                mx0 = fmaxf(mx0, __uint_as_float(sreg[i]));
-                mx1 = fmaxf(mx1, __uint_as_float(sreg[i + 1]));
-                mx2 = fmaxf(mx2, __uint_as_float(sreg[i + 2]));
-                mx3 = fmaxf(mx3, __uint_as_float(sreg[i + 3]));
-            }
-            const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * scale;       // scale > 0
-            if (warp == 4) NATS_STAMP(0, jt, 2);
-            // online softmax with lazy rescaling: the reference maximum only moves when the row max grew by > threshold
-            float alpha = 1.f;
-            bool need = false;
-            if (mx > m_ref + kRescaleThreshold) {           // also true for the first visible tile (m_ref = -inf)
-                if (m_ref != -INFINITY) {                   // a row without visible entries so far has O = 0, l = 0
-                    alpha = ex2(m_ref - mx);
-                    l_sum *= alpha;
-                    need = true;
-                }
-                m_ref = mx;
-            }
-            if (jt > 0 && __any_sync(0xffffffffu, need)) {
-                // O_h of the previous tiles is complete (the commit behind S_h covers every earlier MMA): rescale it
+                        for (int w = 0; w < 4; ++w) bits[w] = range_mask(0, nvis, w);
+                        const int c_first = k0 / p.C, c_last = min((k0 + kTile - 1) / p.C, p.Nc - 1);
 #pragma unroll 1
-                for (int c = 0; c < D / 32; ++c) {
-                    uint32_t r[32];
-                    tmem_ld32(tO + c * 32, r);
+                        for (int cc = c_first; cc <= c_last; ++cc) {
+                            if (qi > lim[cc]) {
+                                const int lo = max(cc * p.C - k0, 0), hi = min((cc + 1) * p.C - k0, kTile);
+#pragma unroll
+                                for (int w = 0; w < 4; ++w) bits[w] &= ~range_mask(lo, hi, w);
+                            }
+                        }
+                    }
+                    ok = mbar_wait(smem_u32(&sm.bar_s_full[h]), gh & 1, abort_flag, p.status, kErrSFull);
+                    if (!ok) break;
+                    tc_fence_after();
+                    // the whole score row of this thread in registers: four loads in flight, one wait
+                    uint32_t sreg[128];
+                    tmem_ld32(tS + 0, *reinterpret_cast<uint32_t(*)[32]>(&sreg[0]));
+                    tmem_ld32(tS + 32, *reinterpret_cast<uint32_t(*)[32]>(&sreg[32]));
+                    tmem_ld32(tS + 64, *reinterpret_cast<uint32_t(*)[32]>(&sreg[64]));
+                    tmem_ld32(tS + 96, *reinterpret_cast<uint32_t(*)[32]>(&sreg[96]));
                     tc_wait_ld();
+                    if (partial) {
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-                    tmem_st32(tO + c * 32, r);
-                }
-            }
-            const float m_neg = (m_ref == -INFINITY) ? 0.f : -m_ref;
-            if (warp == 4) NATS_STAMP(0, jt, 3);
-            // P = exp2(S * scale - m), row sum in fp32, P packed to bf16 over the first 64 columns of S_h
-            float ls0 = 0.f, ls1 = 0.f;
+                        for (int i = 0; i < 128; ++i)
+                            if (!((bits[i >> 5] >> (i & 31)) & 1u)) sreg[i] = 0xff800000u;      // -inf: exp2 gives exactly 0
+                    }
+                    float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                uint32_t pk[16];
-#pragma unroll
-                for (int i = 0; i < 32; i += 2) {
-                    const float p0 = ex2(fmaf(__uint_as_float(sreg[c * 32 + i]), scale, m_neg));
-                    const float p1 = ex2(fmaf(__uint_as_float(sreg[c * 32 + i + 1]), scale, m_neg));
-                    ls0 += p0;
-                    ls1 += p1;
-                    pk[i / 2] = pack_bf16(p0, p1);
-                }
-                tmem_st16(tS + c * 16, pk);
-            }
-            l_sum += ls0 + ls1;
-            if (warp == 4) NATS_STAMP(0, jt, 4);
-            tc_wait_st();
-            tc_fence_before();
-            mbar_arrive(smem_u32(&sm.bar_p_full[h]));
-            if (warp == 4) NATS_STAMP(0, jt, 5);
-        }
-        // epilogue: O / l -> bf16 -> global
-        if (ok && n_kept > 0) ok = mbar_wait(smem_u32(&sm.bar_o_full[h]), 0, abort_flag, p.status, kErrOFull);
-        if (ok && n_kept > 0) {
-            tc_fence_after();
-            const float inv = l_sum > 0.f ? 1.f / l_sum : 0.f;
-            __nv_bfloat16* orow = p.o + (((size_t)b * p.Hq + head0 + h) * p.N + qi) * D;
+                    for (int i = 0; i < 128; i += 4) {
+                        mx0 = fmaxf(mx0, __uint_as_float(sreg[i]));
+                        mx1 = fmaxf(mx1, __uint_as_float(sreg[i + 1]));
+                        mx2 = fmaxf(mx2, __uint_as_float(sreg[i + 2]));
+                        mx3 = fmaxf(mx3, __uint_as_float(sreg[i + 3]));
+                    }
+                    const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * scale;       // scale > 0
+                    // online softmax with lazy rescaling: the reference maximum only moves when the row max grew by > threshold
+                    float alpha = 1.f;
+                    bool need = false;
+                    if (mx > m_ref + kRescaleThreshold) {           // also true for the first visible tile (m_ref = -inf)
+                        if (m_ref != -INFINITY) {                   // a row without visible entries so far has O = 0, l = 0
+                            alpha = ex2(m_ref - mx);
+                            l_sum *= alpha;
+                            need = true;
+                        }
+                        m_ref = mx;
+                    }
+                    if (jt > 0 && __any_sync(0xffffffffu, need)) {
+                        // O_h of the previous tiles is complete (the commit behind S_h covers every earlier MMA): rescale it
 #pragma unroll 1
-            for (int c = 0; c < D / 32; ++c) {
-                uint32_t r[32];
-                tmem_ld32(tO + c * 32, r);
-                tc_wait_ld();
-                if (qi < p.N) {
+                        for (int c = 0; c < D / 32; ++c) {
+                            uint32_t r[32];
+                            tmem_ld32(tO + c * 32, r);
+                            tc_wait_ld();
 #pragma unroll
-                    for (int i = 0; i < 32; i += 8) {
-                        uint4 w;
-                        w.x = pack_bf16(__uint_as_float(r[i]) * inv, __uint_as_float(r[i + 1]) * inv);
-                        w.y = pack_bf16(__uint_as_float(r[i + 2]) * inv, __uint_as_float(r[i + 3]) * inv);
-                        w.z = pack_bf16(__uint_as_float(r[i + 4]) * inv, __uint_as_float(r[i + 5]) * inv);
-                        w.w = pack_bf16(__uint_as_float(r[i + 6]) * inv, __uint_as_float(r[i + 7]) * inv);
-                        st16(orow + c * 32 + i, w);
+                            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+                            tmem_st32(tO + c * 32, r);
+                        }
+                    }
+                    const float m_neg = (m_ref == -INFINITY) ? 0.f : -m_ref;
+                    // P = exp2(S * scale - m), row sum in fp32, P packed to bf16 over the first 64 columns of S_h
+                    float ls0 = 0.f, ls1 = 0.f;
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        uint32_t pk[16];
+#pragma unroll
+                        for (int i = 0; i < 32; i += 2) {
+                            const float p0 = ex2(fmaf(__uint_as_float(sreg[c * 32 + i]), scale, m_neg));
+                            const float p1 = ex2(fmaf(__uint_as_float(sreg[c * 32 + i + 1]), scale, m_neg));
+                            ls0 += p0;
+                            ls1 += p1;
+                            pk[i / 2] = pack_bf16(p0, p1);
+                        }
+                        tmem_st16(tS + c * 16, pk);
+                    }
+                    l_sum += ls0 + ls1;
+                    tc_wait_st();
+                    tc_fence_before();
+                    mbar_arrive(smem_u32(&sm.bar_p_full[h]));
+                }
+                // epilogue: O / l -> bf16 -> global; O_h is handed back to the issuer as soon as it sits in registers
+                if (ok && n_kept > 0) ok = mbar_wait(smem_u32(&sm.bar_o_full[h]), na & 1, abort_flag, p.status, kErrOFull);
+                if (ok && n_kept > 0) {
+                    tc_fence_after();
+                    const float inv = l_sum > 0.f ? 1.f / l_sum : 0.f;
+                    __nv_bfloat16* orow = p.o + (((size_t)hd.b * p.Hq + hd.head0 + h) * p.N + qi) * D;
+                    uint32_t oreg[D];
+#pragma unroll
+                    for (int c = 0; c < D / 32; ++c) tmem_ld32(tO + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&oreg[c * 32]));
+                    tc_wait_ld();
+                    tc_fence_before();
+                    mbar_arrive(smem_u32(&sm.bar_o_empty[h]));
+                    if (qi < p.N) {
+#pragma unroll
+                        for (int i = 0; i < D; i += 8) {
+                            uint4 w;
+                            w.x = pack_bf16(__uint_as_float(oreg[i]) * inv, __uint_as_float(oreg[i + 1]) * inv);
+                            w.y = pack_bf16(__uint_as_float(oreg[i + 2]) * inv, __uint_as_float(oreg[i + 3]) * inv);
+                            w.z = pack_bf16(__uint_as_float(oreg[i + 4]) * inv, __uint_as_float(oreg[i + 5]) * inv);
+                            w.w = pack_bf16(__uint_as_float(oreg[i + 6]) * inv, __uint_as_float(oreg[i + 7]) * inv);
+                            st16(orow + i, w);
+                        }
                     }
                 }
+                ++na;
             }
+            __syncwarp();
+            if (ok && lane == 0) mbar_arrive(smem_u32(&sm.bar_list_empty[slot]));
         }
     }
     // ---- teardown ----
-    if (warp == 1) NATS_STAMP(1, 62, 7);
     tc_fence_before();
     __syncthreads();
-    if (warp == 1) NATS_STAMP(1, 63, 7);
     if (warp == 1) {
         if (sm.abort_flag) {
             // MMAs may still be running: give them time before the accumulator columns are released
@@ -613,14 +685,15 @@ static int make_map(CUtensorMap* map, const void* base, int heads, int N, int D)
     return NATS_OK;
 }
 
-struct PrefillWs { size_t lim, tmax, tmin, total; };
+struct PrefillWs { size_t lim, tmax, tmin, counter, total; };
 static PrefillWs prefill_ws(int B, int Hkv, int N, int C) {
     PrefillWs w;
     const size_t Nc = cdiv(N, C), Nt = cdiv(N, kTile);
     w.lim = 0;
     w.tmax = align_up((size_t)B * Hkv * Nc * 4, 256);
     w.tmin = w.tmax + align_up((size_t)B * Hkv * Nt * 4, 256);
-    w.total = w.tmin + align_up((size_t)B * Hkv * Nt * 4, 256);
+    w.counter = w.tmin + align_up((size_t)B * Hkv * Nt * 4, 256);
+    w.total = w.counter + 256;
     return w;
 }
 
@@ -633,7 +706,12 @@ static int launch_prefill(const CUtensorMap& mq, const CUtensorMap& mk, const CU
         NATS_CHECK_CUDA(cudaFuncSetAttribute(prefill_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         attr_set = true;
     }
-    dim3 grid(p.Nt, p.Hkv * p.n_groups, B);
+    int dev = 0, sms = 0;
+    NATS_CHECK_CUDA(cudaGetDevice(&dev));
+    NATS_CHECK_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    NATS_CHECK_CUDA(cudaMemsetAsync(p.work_counter, 0, sizeof(int32_t), st));
+    const int grid = p.total_items < sms ? p.total_items : sms;      // one persistent CTA per SM
+    (void)B;
     prefill_kernel<D><<<grid, kPrefillThreads, smem, st>>>(mq, mk, mv, p);
     NATS_CHECK_CUDA(cudaGetLastError());
     return NATS_OK;
@@ -677,6 +755,10 @@ extern "C" __attribute__((visibility("default"))) int nats_b200_prefill_fwd(cons
     p.o = (__nv_bfloat16*)d_o; p.lim = lim; p.tile_max = tmax; p.tile_min = tmin; p.status = d_status;
     p.Hq = Hq; p.Hkv = Hkv; p.N = N; p.C = C; p.Nc = cdiv(N, C); p.Nt = cdiv(N, kTile);
     p.nrep = Hq / Hkv; p.n_groups = (p.nrep + 1) / 2;
+    p.work_counter = (int32_t*)(ws + w.counter);
+    const long long items = (long long)B * Hkv * p.n_groups * p.Nt;
+    NATS_CHECK_ARG(items <= 0x7fffffffLL - 65536, "too many work items (%lld)", items);
+    p.total_items = (int)items;
     p.scale_log2 = sm_scale * 1.4426950408889634f;
     if (D == 64) return launch_prefill<64>(mq, mk, mv, p, B, (cudaStream_t)stream);
     return launch_prefill<128>(mq, mk, mv, p, B, (cudaStream_t)stream);
@@ -733,8 +815,3 @@ extern "C" __attribute__((visibility("default"))) int nats_b200_prefill_fwd_stat
                                  nats::kStaticScratchBytes, d_kept_tiles, d_status, stream);
 }
 
-#ifdef NATS_TRACE
-extern "C" __attribute__((visibility("default"))) int nats_b200_debug_trace(long long* host_out) {
-    return (int)cudaMemcpyFromSymbol(host_out, nats::g_trace, sizeof(long long) * 2 * 64 * 8);
-}
-#endif
