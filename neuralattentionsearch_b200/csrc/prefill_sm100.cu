@@ -24,8 +24,23 @@
 namespace nats {
 
 constexpr int kPrefillThreads = 384;
-constexpr int kStages = 2;
-constexpr uint32_t kBoxBytes = 128 * 64 * 2;            // one TMA box: 128 rows x 64 bf16, 128-byte swizzled
+#ifndef NATS_REGS_LOW
+#define NATS_REGS_LOW 104
+#endif
+#ifndef NATS_REGS_HIGH
+#define NATS_REGS_HIGH 200
+#endif
+// setmaxnreg split: 128 * low + 256 * high must not exceed the 384 * 168 registers of the launch
+constexpr int kRegsLow = NATS_REGS_LOW, kRegsHigh = NATS_REGS_HIGH;
+static_assert(128 * kRegsLow + 256 * kRegsHigh <= 384 * 168, "setmaxnreg budget");
+#ifndef NATS_PINGPONG
+#define NATS_PINGPONG 1
+#endif
+constexpr bool kPingPong = NATS_PINGPONG != 0;   // the two heads' warps that share a scheduler take turns on the MUFU pipe
+constexpr int kStages = 4;                              // K/V ring depth, in 64-row sub-tiles
+constexpr int kSub = 64;                                // key columns per sub-tile (two per kept 128-column tile)
+constexpr uint32_t kQBoxBytes = 128 * 64 * 2;           // one TMA box of Q: 128 rows x 64 bf16, 128-byte swizzled
+constexpr uint32_t kKvBoxBytes = kSub * 64 * 2;         // one TMA box of K or V: 64 rows x 64 bf16
 #ifndef NATS_RELAX_NS
 #define NATS_RELAX_NS 200
 #endif
@@ -37,7 +52,7 @@ constexpr int kRelaxProdNs = NATS_RELAX_PROD_NS;
 constexpr float kRescaleThreshold = 8.0f;               // log2 units: O is rescaled only when the row max grows by more
 constexpr unsigned long long kWaitLimitNs = 400ull * 1000ull * 1000ull;
 
-enum : int { kErrQ = 1, kErrKFull, kErrVFull, kErrKEmpty, kErrVEmpty, kErrSFull, kErrPFull, kErrOFull, kErrTurn, kErrList, kErrOEmpty };
+enum : int { kErrQ = 1, kErrKFull, kErrVFull, kErrKEmpty, kErrVEmpty, kErrSFull, kErrPFull, kErrOFull, kErrTurn, kErrList, kErrOEmpty, kErrPvDone, kErrMufu };
 
 struct PrefillParams {
     __nv_bfloat16* o;                 // [B,Hq,N,D]
@@ -215,21 +230,21 @@ struct ItemHeader {
     int b, bh;      // batch index, b * Hkv + kv-head
     int head0;      // query head of slot 0
     int nslots;     // 1 or 2 query heads in this item
-    int n_kept;     // kept KV tiles
+    int n_kept;     // kept 128-column KV tiles (each is processed as two 64-column sub-tiles)
     int pad;
 };
 
 template <int D>
 struct __align__(1024) PrefillSmem {
     uint8_t q[2][128 * D * 2];             // one tile per head slot; D/64 boxes of 16 KB each
-    uint8_t k[kStages][128 * D * 2];
-    uint8_t v[kStages][128 * D * 2];
+    uint8_t kv[kStages][2][kSub * D * 2];  // per stage: K sub-tile, V sub-tile; D/64 boxes of 8 KB each
     uint16_t list[2][kMaxTiles];           // kept KV tiles of an item, ascending; bit 15 = needs element masking (double buffered)
     ItemHeader item[2];
     unsigned long long bar_q_full, bar_q_empty;
-    unsigned long long bar_k_full[kStages], bar_k_empty[kStages], bar_v_full[kStages], bar_v_empty[kStages];
-    unsigned long long bar_s_full[2], bar_p_full[2], bar_o_full[2], bar_o_empty[2], bar_turn[2];
+    unsigned long long bar_kv_full[kStages], bar_kv_empty[kStages];
+    unsigned long long bar_s_full[2][2], bar_p_full[2][2], bar_pv_done[2], bar_o_full[2], bar_o_empty[2];
     unsigned long long bar_list_full[2], bar_list_empty[2];
+    unsigned long long bar_mufu[2][4];     // [head slot][warp quarter]: permission to run the exponentials
     uint32_t tmem_base;
     int abort_flag;
 };
@@ -239,8 +254,13 @@ constexpr int kListConsumers = 1 + 2 + 8;     // producer, two issuers, one lane
 // Persistent kernel: every CTA takes work items (query tile x kv-head x head pair) from a global counter until none is
 // left.  Per-item set-up (kept-tile list, Q load) and tear-down (O -> global) overlap the main loops of the neighbouring
 // items: warp 3 prepares the list of the next item while the current one runs, the producer streams the next item's K/V
-// through the same rings without a bubble, Q of the next item is loaded as soon as the last Q.K^T of the current one
+// through the same ring without a bubble, Q of the next item is loaded as soon as the last Q.K^T of the current one
 // has completed, and a head's epilogue only delays that head's own chain.
+//
+// A kept 128-column KV tile is processed as two 64-column sub-tiles, and every head has TWO score buffers in TMEM
+// (S_a, S_b: 64 columns each) next to its 128-column O accumulator.  S = Q.K^T of sub-tile u+1 is therefore computed
+// while the softmax warps still work on sub-tile u: the softmax of a head runs back to back and only O += P.V waits for
+// it, so the tensor pipe is kept busy by two independent chains instead of being stalled by one softmax latency per tile.
 template <int D>
 __global__ void __launch_bounds__(kPrefillThreads, 1)
 prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
@@ -248,8 +268,9 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     extern __shared__ uint8_t smem_raw[];
     PrefillSmem<D>& sm = *reinterpret_cast<PrefillSmem<D>*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     constexpr int NBOX = D / 64;                       // TMA boxes per tile
-    constexpr uint32_t TILE_BYTES = NBOX * kBoxBytes;
-    constexpr uint32_t IDESC_QK = instr_desc(128, false);
+    constexpr uint32_t Q_BYTES = NBOX * kQBoxBytes;    // one Q tile (128 rows)
+    constexpr uint32_t SUB_BYTES = NBOX * kKvBoxBytes; // one K or V sub-tile (64 rows)
+    constexpr uint32_t IDESC_QK = instr_desc(kSub, false);
     constexpr uint32_t IDESC_PV = instr_desc(D, true);
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -264,19 +285,20 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         mbar_init(smem_u32(&sm.bar_q_full), 1);
         mbar_init(smem_u32(&sm.bar_q_empty), 2);                   // one commit per MMA issuer
         for (int s = 0; s < kStages; ++s) {
-            mbar_init(smem_u32(&sm.bar_k_full[s]), 1);
-            mbar_init(smem_u32(&sm.bar_k_empty[s]), 2);
-            mbar_init(smem_u32(&sm.bar_v_full[s]), 1);
-            mbar_init(smem_u32(&sm.bar_v_empty[s]), 2);
+            mbar_init(smem_u32(&sm.bar_kv_full[s]), 1);
+            mbar_init(smem_u32(&sm.bar_kv_empty[s]), 2);
         }
         for (int h = 0; h < 2; ++h) {
-            mbar_init(smem_u32(&sm.bar_s_full[h]), 1);
-            mbar_init(smem_u32(&sm.bar_p_full[h]), 128);
+            for (int x = 0; x < 2; ++x) {
+                mbar_init(smem_u32(&sm.bar_s_full[h][x]), 1);
+                mbar_init(smem_u32(&sm.bar_p_full[h][x]), 128);
+            }
+            mbar_init(smem_u32(&sm.bar_pv_done[h]), 1);
             mbar_init(smem_u32(&sm.bar_o_full[h]), 1);
             mbar_init(smem_u32(&sm.bar_o_empty[h]), 128);
-            mbar_init(smem_u32(&sm.bar_turn[h]), 1);
             mbar_init(smem_u32(&sm.bar_list_full[h]), 1);
             mbar_init(smem_u32(&sm.bar_list_empty[h]), kListConsumers);
+            for (int x = 0; x < 4; ++x) mbar_init(smem_u32(&sm.bar_mufu[h][x]), 1);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         prefetch_tmap(&map_q);
@@ -292,9 +314,9 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     tc_fence_after();
     const uint32_t tmem = sm.tmem_base;
 
-    // Register budget: the softmax warpgroups hold a whole score row per thread (setmaxnreg.inc at the top of their
-    // branch), the producer / issuer / scheduler warpgroup needs little and gives registers back.
-    if (warp < 4) asm volatile("setmaxnreg.dec.sync.aligned.u32 48;");      // one site for the whole warpgroup
+    // Register budget: the softmax warpgroups get more registers (setmaxnreg.inc at the top of their branch), the
+    // producer / issuer / scheduler warpgroup needs little and gives registers back.
+    if (warp < 4) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsLow));      // one site for the whole warpgroup
 
     if (warp == 3) {
         // =============================== scheduler: next work item and its kept-tile list ===============================
@@ -343,8 +365,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         }
     } else if (warp == 0) {
         // =============================== TMA producer ===============================
-        uint32_t g = 0;                                 // tiles pushed through the K / V rings so far (all items)
-        uint32_t issued_k = 0, issued_v = 0;
+        uint32_t g = 0;                                 // sub-tiles pushed through the K/V ring so far (all items)
         bool ok = true;
         for (int ic = 0; ok; ++ic) {
             const int slot = ic & 1;
@@ -356,156 +377,144 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             if (ic > 0) ok = mbar_wait(smem_u32(&sm.bar_q_empty), (ic - 1) & 1, abort_flag, p.status, kErrQ);
             if (!ok) break;
             if (lane == 0) {
-                mbar_expect_tx(smem_u32(&sm.bar_q_full), hd.nslots * TILE_BYTES);
+                mbar_expect_tx(smem_u32(&sm.bar_q_full), hd.nslots * Q_BYTES);
                 for (int h = 0; h < hd.nslots; ++h)
                     for (int x = 0; x < NBOX; ++x)
-                        tma_load_3d(smem_u32(&sm.q[h][x * kBoxBytes]), &map_q, smem_u32(&sm.bar_q_full), x * 64, hd.t * kTile,
+                        tma_load_3d(smem_u32(&sm.q[h][x * kQBoxBytes]), &map_q, smem_u32(&sm.bar_q_full), x * 64, hd.t * kTile,
                                     hd.b * p.Hq + hd.head0 + h);
             }
-            for (int jt = 0; jt < hd.n_kept && ok; ++jt, ++g) {
-                const int kt = sm.list[slot][jt] & 0x7fff;
+            for (int u = 0; u < 2 * hd.n_kept && ok; ++u, ++g) {
+                const int kt = sm.list[slot][u >> 1] & 0x7fff;
+                const int row0 = kt * kTile + (u & 1) * kSub;
                 const int s = g % kStages;
                 const uint32_t ph = (g / kStages) & 1;
-                if (g >= kStages) ok = mbar_wait<kRelaxProdNs>(smem_u32(&sm.bar_k_empty[s]), ph ^ 1, abort_flag, p.status, kErrKEmpty);
+                if (g >= kStages) ok = mbar_wait<kRelaxProdNs>(smem_u32(&sm.bar_kv_empty[s]), ph ^ 1, abort_flag, p.status, kErrKEmpty);
                 if (!ok) break;
                 if (lane == 0) {
-                    mbar_expect_tx(smem_u32(&sm.bar_k_full[s]), TILE_BYTES);
+                    mbar_expect_tx(smem_u32(&sm.bar_kv_full[s]), 2 * SUB_BYTES);
                     for (int x = 0; x < NBOX; ++x)
-                        tma_load_3d(smem_u32(&sm.k[s][x * kBoxBytes]), &map_k, smem_u32(&sm.bar_k_full[s]), x * 64, kt * kTile, hd.bh);
-                }
-                ++issued_k;
-                if (g >= kStages) ok = mbar_wait<kRelaxProdNs>(smem_u32(&sm.bar_v_empty[s]), ph ^ 1, abort_flag, p.status, kErrVEmpty);
-                if (!ok) break;
-                if (lane == 0) {
-                    mbar_expect_tx(smem_u32(&sm.bar_v_full[s]), TILE_BYTES);
+                        tma_load_3d(smem_u32(&sm.kv[s][0][x * kKvBoxBytes]), &map_k, smem_u32(&sm.bar_kv_full[s]), x * 64, row0, hd.bh);
                     for (int x = 0; x < NBOX; ++x)
-                        tma_load_3d(smem_u32(&sm.v[s][x * kBoxBytes]), &map_v, smem_u32(&sm.bar_v_full[s]), x * 64, kt * kTile, hd.bh);
+                        tma_load_3d(smem_u32(&sm.kv[s][1][x * kKvBoxBytes]), &map_v, smem_u32(&sm.bar_kv_full[s]), x * 64, row0, hd.bh);
                 }
-                ++issued_v;
                 __syncwarp();
             }
             if (ok && lane == 0) mbar_arrive(smem_u32(&sm.bar_list_empty[slot]));
         }
         if (!ok) {
             // given up: let copies that are still in flight land before the shared memory is released
-            for (uint32_t x = issued_k > kStages ? issued_k - kStages : 0; x < issued_k; ++x)
-                mbar_wait(smem_u32(&sm.bar_k_full[x % kStages]), (x / kStages) & 1, nullptr, p.status, kErrKFull);
-            for (uint32_t x = issued_v > kStages ? issued_v - kStages : 0; x < issued_v; ++x)
-                mbar_wait(smem_u32(&sm.bar_v_full[x % kStages]), (x / kStages) & 1, nullptr, p.status, kErrVFull);
+            for (uint32_t x = g > kStages ? g - kStages : 0; x < g; ++x)
+                mbar_wait(smem_u32(&sm.bar_kv_full[x % kStages]), (x / kStages) & 1, nullptr, p.status, kErrKFull);
         }
     } else if (warp == 1 || warp == 2) {
         // =============================== MMA issuers: warp 1 for head slot 0, warp 2 for head slot 1 ===============================
-        // Each issuer owns the chain of its head: O_h += P_h.V for tile j, then S_h = Q_h.K^T for tile j+1 (which may only
-        // overwrite S_h once the MMA reading P_h from it has been issued).  The two issuers take turns (a token passed
-        // through bar_turn): the heads stay half a period apart, so one head's exponentials overlap the other head's MMAs
-        // instead of both competing for the same unit at once.  K/V stages and Q are released when both issuers have
-        // committed; an issuer whose head slot is empty in an item (odd group size) only keeps the barrier counts going.
+        // Per head and 64-column sub-tile u:  S[u & 1] = Q_h.K_u^T  (issued two sub-tiles ahead of the softmax) and
+        // O_h += P_u.V_u once the softmax warps have written P_u over S[u & 1].  S[u & 1] is overwritten by sub-tile u + 2
+        // only after the MMA that reads P_u has been issued (same thread, so the tensor pipe keeps the order).
+        // A K/V stage is released when both issuers have committed its P.V; an issuer whose head slot is empty in an item
+        // (odd group size) only keeps the barrier counts going.
         const int h = warp - 1;
-        constexpr uint32_t TILE16 = TILE_BYTES >> 4;
-        const uint64_t q_desc = smem_desc(smem_u32(&sm.q[0][0]), 16, 1024) + (uint64_t)(h * TILE16);
-        const uint64_t k_desc0 = smem_desc(smem_u32(&sm.k[0][0]), 16, 1024);
-        const uint64_t v_desc0 = smem_desc(smem_u32(&sm.v[0][0]), kBoxBytes, 1024);
-        const uint32_t dS = tmem + h * 128, dO = tmem + 256 + h * 128;
-        auto issue_qk = [&](int s) {
-            // S_h[128 x 128] = Q_h[128 x D] . K[128 x D]^T : D/16 MMAs of K = 16
-            const uint64_t kd = k_desc0 + (uint64_t)(s * TILE16);
+        constexpr uint32_t Q16 = Q_BYTES >> 4, SUB16 = SUB_BYTES >> 4, STAGE16 = (2 * SUB_BYTES) >> 4;
+        const uint64_t q_desc = smem_desc(smem_u32(&sm.q[0][0]), 16, 1024) + (uint64_t)(h * Q16);
+        const uint64_t k_desc0 = smem_desc(smem_u32(&sm.kv[0][0][0]), 16, 1024);
+        const uint64_t v_desc0 = smem_desc(smem_u32(&sm.kv[0][1][0]), kKvBoxBytes, 1024);
+        const uint32_t tS = tmem + h * 256, tO = tmem + h * 256 + 128;
+        auto issue_qk = [&](int s, int buf) {
+            // S[buf][128 x 64] = Q_h[128 x D] . K_u[64 x D]^T : D/16 MMAs of K = 16
+            const uint64_t kd = k_desc0 + (uint64_t)(s * STAGE16);
+            const uint32_t dS = tS + buf * kSub;
             mma_ss<0>(dS, q_desc, kd, IDESC_QK);
 #pragma unroll
             for (int ks = 1; ks < D / 16; ++ks) {
-                const uint32_t off16 = ((ks / 4) * kBoxBytes + (ks % 4) * 32) >> 4;
-                mma_ss<1>(dS, q_desc + off16, kd + off16, IDESC_QK);
+                const uint32_t qoff = ((ks / 4) * kQBoxBytes + (ks % 4) * 32) >> 4;
+                const uint32_t koff = ((ks / 4) * kKvBoxBytes + (ks % 4) * 32) >> 4;
+                mma_ss<1>(dS, q_desc + qoff, kd + koff, IDESC_QK);
             }
         };
-        auto issue_pv = [&](int s, bool first) {
-            // O_h[128 x D] (+)= P_h[128 x 128] . V[128 x D] : 8 MMAs of K = 16; V is MN-major (D contiguous)
-            const uint64_t vd = v_desc0 + (uint64_t)(s * TILE16);
-            mma_ts(dO, dS, vd, IDESC_PV, first ? 0u : 1u);
+        auto issue_pv = [&](int s, int buf, bool first) {
+            // O_h[128 x D] (+)= P_u[128 x 64] . V_u[64 x D] : 4 MMAs of K = 16; V is MN-major (D contiguous)
+            const uint64_t vd = v_desc0 + (uint64_t)(s * STAGE16);
+            const uint32_t aP = tS + buf * kSub;
+            mma_ts(tO, aP, vd, IDESC_PV, first ? 0u : 1u);
 #pragma unroll
-            for (int ks = 1; ks < 8; ++ks) mma_ts(dO, dS + ks * 8, vd + (uint64_t)(ks * (2048 >> 4)), IDESC_PV, 1u);
+            for (int ks = 1; ks < kSub / 16; ++ks) mma_ts(tO, aP + ks * 8, vd + (uint64_t)(ks * (2048 >> 4)), IDESC_PV, 1u);
         };
-        uint32_t g = 0;          // tiles through the K / V rings (all items, both issuers count alike)
-        uint32_t gh = 0;         // tiles of this head (items in which its slot is used)
+        (void)SUB16;
+        uint32_t g = 0;          // sub-tiles through the K/V ring (all items, both issuers count alike)
+        uint32_t gu = 0;         // sub-tiles of this head (items in which its slot is used); even at every item start
         uint32_t na = 0;         // items in which this head's slot was used
-        uint32_t turns = 0;      // turns taken in two-head items
         bool ok = true;
-        auto take_turn = [&]() {
-            // issuer 0 follows issuer 1's previous turn, issuer 1 follows issuer 0's turn of the same number
-            if (h == 0) return turns == 0 ? true : mbar_wait(smem_u32(&sm.bar_turn[0]), (turns - 1) & 1, abort_flag, p.status, kErrTurn);
-            return mbar_wait(smem_u32(&sm.bar_turn[1]), turns & 1, abort_flag, p.status, kErrTurn);
-        };
         for (int ic = 0; ok; ++ic) {
             const int slot = ic & 1;
             ok = mbar_wait(smem_u32(&sm.bar_list_full[slot]), (ic >> 1) & 1, abort_flag, p.status, kErrList);
             if (!ok) break;
             const ItemHeader hd = sm.item[slot];
             if (!hd.valid) break;
-            const int n = hd.n_kept;
-            const bool active = h < hd.nslots, two = hd.nslots == 2;
+            const int n2 = 2 * hd.n_kept;
+            const bool active = h < hd.nslots;
             if (active) ok = mbar_wait(smem_u32(&sm.bar_q_full), ic & 1, abort_flag, p.status, kErrQ);
-            // ---- first tile: S_h = Q_h.K^T ----
-            if (ok) ok = mbar_wait(smem_u32(&sm.bar_k_full[g % kStages]), (g / kStages) & 1, abort_flag, p.status, kErrKFull);
-            if (ok && active && two) ok = take_turn();
-            if (!ok) break;
-            tc_fence_after();
-            if (lane == 0) {
-                if (active) {
-                    issue_qk(g % kStages);
-                    tc_commit(smem_u32(&sm.bar_s_full[h]));
-                }
-                tc_commit(smem_u32(&sm.bar_k_empty[g % kStages]));
-                if (n == 1) tc_commit(smem_u32(&sm.bar_q_empty));
-                if (active && two) mbar_arrive(smem_u32(&sm.bar_turn[1 - h]));
-            }
-            if (active && two) ++turns;
-            __syncwarp();
-            // ---- tiles ----
-            for (int jt = 0; jt < n && ok; ++jt, ++g) {
-                const int s = g % kStages;
-                const uint32_t ph = (g / kStages) & 1;
-                const bool has_next = jt + 1 < n;
-                const int sn = (g + 1) % kStages;
-                const uint32_t phn = ((g + 1) / kStages) & 1;
-                ok = mbar_wait(smem_u32(&sm.bar_v_full[s]), ph, abort_flag, p.status, kErrVFull);
-                if (ok && has_next) ok = mbar_wait(smem_u32(&sm.bar_k_full[sn]), phn, abort_flag, p.status, kErrKFull);
-                if (ok && active) ok = mbar_wait(smem_u32(&sm.bar_p_full[h]), gh & 1, abort_flag, p.status, kErrPFull);
-                // the first P.V of an item overwrites O_h: the previous item's epilogue must have read it
-                if (ok && active && jt == 0 && na > 0) ok = mbar_wait(smem_u32(&sm.bar_o_empty[h]), (na - 1) & 1, abort_flag, p.status, kErrOEmpty);
-                if (ok && active && two) ok = take_turn();
+            // ---- the first two score buffers ----
+            for (int x = 0; x < 2 && ok; ++x) {
+                const uint32_t gx = g + x;
+                ok = mbar_wait(smem_u32(&sm.bar_kv_full[gx % kStages]), (gx / kStages) & 1, abort_flag, p.status, kErrKFull);
                 if (!ok) break;
                 tc_fence_after();
                 if (lane == 0) {
                     if (active) {
-                        issue_pv(s, jt == 0);
-                        if (!has_next) tc_commit(smem_u32(&sm.bar_o_full[h]));
+                        issue_qk(gx % kStages, x);
+                        tc_commit(smem_u32(&sm.bar_s_full[h][x]));
                     }
-                    tc_commit(smem_u32(&sm.bar_v_empty[s]));
-                    if (has_next) {
-                        if (active) {
-                            issue_qk(sn);
-                            tc_commit(smem_u32(&sm.bar_s_full[h]));
-                        }
-                        tc_commit(smem_u32(&sm.bar_k_empty[sn]));
-                        if (jt + 2 == n) tc_commit(smem_u32(&sm.bar_q_empty));      // that was the last Q.K^T of the item
-                    }
-                    if (active && two) mbar_arrive(smem_u32(&sm.bar_turn[1 - h]));
+                    if (x == 1 && n2 == 2) tc_commit(smem_u32(&sm.bar_q_empty));
                 }
-                if (active && two) ++turns;
-                if (active) ++gh;
                 __syncwarp();
             }
-            if (active) ++na;
+            // ---- sub-tiles ----
+            for (int u = 0; u < n2 && ok; ++u) {
+                const uint32_t gs = g + u;
+                const int s = gs % kStages, buf = u & 1;
+                const bool more = u + 2 < n2;
+                if (active) {
+                    ok = mbar_wait(smem_u32(&sm.bar_p_full[h][buf]), ((gu + u) >> 1) & 1, abort_flag, p.status, kErrPFull);
+                    // the first P.V of an item overwrites O_h: the previous item's epilogue must have read it
+                    if (ok && u == 0 && na > 0) ok = mbar_wait(smem_u32(&sm.bar_o_empty[h]), (na - 1) & 1, abort_flag, p.status, kErrOEmpty);
+                } else {
+                    ok = mbar_wait(smem_u32(&sm.bar_kv_full[s]), (gs / kStages) & 1, abort_flag, p.status, kErrKFull);
+                }
+                if (ok && more) ok = mbar_wait(smem_u32(&sm.bar_kv_full[(gs + 2) % kStages]), ((gs + 2) / kStages) & 1, abort_flag, p.status, kErrKFull);
+                if (!ok) break;
+                tc_fence_after();
+                if (lane == 0) {
+                    if (active) {
+                        issue_pv(s, buf, u == 0);
+                        tc_commit(smem_u32(&sm.bar_pv_done[h]));
+                        if (u == n2 - 1) tc_commit(smem_u32(&sm.bar_o_full[h]));
+                    }
+                    tc_commit(smem_u32(&sm.bar_kv_empty[s]));
+                    if (more) {
+                        if (active) {
+                            issue_qk((gs + 2) % kStages, buf);
+                            tc_commit(smem_u32(&sm.bar_s_full[h][buf]));
+                        }
+                        if (u + 3 == n2) tc_commit(smem_u32(&sm.bar_q_empty));      // that was the last Q.K^T of the item
+                    }
+                }
+                __syncwarp();
+            }
+            g += n2;
+            if (active) { gu += n2; ++na; }
             if (ok && lane == 0) mbar_arrive(smem_u32(&sm.bar_list_empty[slot]));
         }
     } else if (warp >= 4) {
         // =============================== softmax + epilogue ===============================
-        asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegsHigh));
         const int h = (warp - 4) / 4;                    // head slot
         const int row = (warp & 3) * 32 + lane;          // query row inside the tile == TMEM lane
         const uint32_t lane_addr = ((uint32_t)((warp & 3) * 32)) << 16;
-        const uint32_t tS = tmem + lane_addr + h * 128;
-        const uint32_t tO = tmem + lane_addr + 256 + h * 128;
+        const uint32_t tS = tmem + lane_addr + h * 256;
+        const uint32_t tO = tmem + lane_addr + h * 256 + 128;
         const float scale = p.scale_log2;
-        uint32_t gh = 0, na = 0;                         // tiles / items of this head so far
+        uint32_t gu = 0, na = 0;                         // sub-tiles / items of this head so far
+        uint32_t rounds = 0;                             // sub-tiles done in two-head items (MUFU turn taking)
         bool ok = true;
         for (int ic = 0; ok; ++ic) {
             const int slot = ic & 1;
@@ -514,51 +523,50 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             const ItemHeader hd = sm.item[slot];
             if (!hd.valid) break;
             if (h < hd.nslots) {
-                const int n_kept = hd.n_kept;
+                const bool pingpong = kPingPong && hd.nslots == 2;
+                const int n2 = 2 * hd.n_kept;
                 const int q_lo = hd.t * kTile;
                 const int qi = q_lo + row;                       // query token index
                 const int32_t* lim = p.lim + (size_t)hd.bh * p.Nc;
                 float m_ref = -INFINITY, l_sum = 0.f;
-                for (int jt = 0; jt < n_kept; ++jt, ++gh) {
-                    const int entry = sm.list[slot][jt];
-                    const int kt = entry & 0x7fff;
+                for (int u = 0; u < n2; ++u, ++gu) {
+                    const int entry = sm.list[slot][u >> 1];
+                    const int buf = u & 1;
+                    const int k0 = (entry & 0x7fff) * kTile + buf * kSub;   // first key column of this sub-tile
                     const bool partial = (entry & 0x8000) != 0;
-                    // visibility bits of this row for the 128 columns of a tile that is not fully visible
-                    uint32_t bits[4] = {0xffffffffu, 0xffffffffu, 0xffffffffu, 0xffffffffu};
+                    // visibility bits of this row for the 64 columns of a sub-tile that is not fully visible
+                    uint32_t bits[2] = {0xffffffffu, 0xffffffffu};
                     if (partial) {
                         // columns this row may see: the causal prefix (and nothing past N), minus every chunk whose row limit is below it
-                        const int k0 = kt * kTile;
-                        const int nvis = max(0, min(min(qi - k0 + 1, p.N - k0), kTile));
+                        const int nvis = max(0, min(min(qi - k0 + 1, p.N - k0), kSub));
 #pragma unroll
-                        for (int w = 0; w < 4; ++w) bits[w] = range_mask(0, nvis, w);
-                        const int c_first = k0 / p.C, c_last = min((k0 + kTile - 1) / p.C, p.Nc - 1);
+                        for (int w = 0; w < 2; ++w) bits[w] = range_mask(0, nvis, w);
+                        const int c_first = k0 / p.C, c_last = min((k0 + kSub - 1) / p.C, p.Nc - 1);
 #pragma unroll 1
                         for (int cc = c_first; cc <= c_last; ++cc) {
                             if (qi > lim[cc]) {
-                                const int lo = max(cc * p.C - k0, 0), hi = min((cc + 1) * p.C - k0, kTile);
+                                const int lo = max(cc * p.C - k0, 0), hi = min((cc + 1) * p.C - k0, kSub);
 #pragma unroll
-                                for (int w = 0; w < 4; ++w) bits[w] &= ~range_mask(lo, hi, w);
+                                for (int w = 0; w < 2; ++w) bits[w] &= ~range_mask(lo, hi, w);
                             }
                         }
                     }
-                    ok = mbar_wait(smem_u32(&sm.bar_s_full[h]), gh & 1, abort_flag, p.status, kErrSFull);
+                    ok = mbar_wait(smem_u32(&sm.bar_s_full[h][buf]), (gu >> 1) & 1, abort_flag, p.status, kErrSFull);
                     if (!ok) break;
                     tc_fence_after();
-                    // the whole score row of this thread in registers: four loads in flight, one wait
-                    uint32_t sreg[128];
-                    tmem_ld32(tS + 0, *reinterpret_cast<uint32_t(*)[32]>(&sreg[0]));
-                    tmem_ld32(tS + 32, *reinterpret_cast<uint32_t(*)[32]>(&sreg[32]));
-                    tmem_ld32(tS + 64, *reinterpret_cast<uint32_t(*)[32]>(&sreg[64]));
-                    tmem_ld32(tS + 96, *reinterpret_cast<uint32_t(*)[32]>(&sreg[96]));
+                    // the score row of this thread in registers: two loads in flight, one wait
+                    uint32_t sreg[kSub];
+                    tmem_ld32(tS + buf * kSub, *reinterpret_cast<uint32_t(*)[32]>(&sreg[0]));
+                    tmem_ld32(tS + buf * kSub + 32, *reinterpret_cast<uint32_t(*)[32]>(&sreg[32]));
                     tc_wait_ld();
                     if (partial) {
 #pragma unroll
-                        for (int i = 0; i < 128; ++i)
+                        for (int i = 0; i < kSub; ++i)
                             if (!((bits[i >> 5] >> (i & 31)) & 1u)) sreg[i] = 0xff800000u;      // -inf: exp2 gives exactly 0
                     }
                     float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll
-                    for (int i = 0; i < 128; i += 4) {
+                    for (int i = 0; i < kSub; i += 4) {
                         mx0 = fmaxf(mx0, __uint_as_float(sreg[i]));
                         mx1 = fmaxf(mx1, __uint_as_float(sreg[i + 1]));
                         mx2 = fmaxf(mx2, __uint_as_float(sreg[i + 2]));
@@ -568,7 +576,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                     // online softmax with lazy rescaling: the reference maximum only moves when the row max grew by > threshold
                     float alpha = 1.f;
                     bool need = false;
-                    if (mx > m_ref + kRescaleThreshold) {           // also true for the first visible tile (m_ref = -inf)
+                    if (mx > m_ref + kRescaleThreshold) {           // also true for the first visible sub-tile (m_ref = -inf)
                         if (m_ref != -INFINITY) {                   // a row without visible entries so far has O = 0, l = 0
                             alpha = ex2(m_ref - mx);
                             l_sum *= alpha;
@@ -576,8 +584,11 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                         }
                         m_ref = mx;
                     }
-                    if (jt > 0 && __any_sync(0xffffffffu, need)) {
-                        // O_h of the previous tiles is complete (the commit behind S_h covers every earlier MMA): rescale it
+                    if (u > 0 && __any_sync(0xffffffffu, need)) {
+                        // O_h is rescaled in place; the P.V of the previous sub-tile has to be complete first
+                        ok = mbar_wait(smem_u32(&sm.bar_pv_done[h]), (gu - 1) & 1, abort_flag, p.status, kErrPvDone);
+                        if (!ok) break;
+                        tc_fence_after();
 #pragma unroll 1
                         for (int c = 0; c < D / 32; ++c) {
                             uint32_t r[32];
@@ -589,10 +600,16 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                         }
                     }
                     const float m_neg = (m_ref == -INFINITY) ? 0.f : -m_ref;
-                    // P = exp2(S * scale - m), row sum in fp32, P packed to bf16 over the first 64 columns of S_h
+                    // The warps of the two heads that sit on the same scheduler share its MUFU pipe: they take turns for the
+                    // exponentials (slot 0 first), so each runs them at the full rate while the other does its loads and maxima.
+                    if (pingpong && (h == 1 || rounds > 0)) {
+                        ok = mbar_wait(smem_u32(&sm.bar_mufu[h][warp & 3]), (h == 1 ? rounds : rounds - 1) & 1, abort_flag, p.status, kErrMufu);
+                        if (!ok) break;
+                    }
+                    // P = exp2(S * scale - m), row sum in fp32, P packed to bf16 over the first 32 columns of this score buffer
                     float ls0 = 0.f, ls1 = 0.f;
 #pragma unroll
-                    for (int c = 0; c < 4; ++c) {
+                    for (int c = 0; c < kSub / 32; ++c) {
                         uint32_t pk[16];
 #pragma unroll
                         for (int i = 0; i < 32; i += 2) {
@@ -602,16 +619,21 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                             ls1 += p1;
                             pk[i / 2] = pack_bf16(p0, p1);
                         }
-                        tmem_st16(tS + c * 16, pk);
+                        tmem_st16(tS + buf * kSub + c * 16, pk);
                     }
                     l_sum += ls0 + ls1;
+                    if (pingpong) {
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(smem_u32(&sm.bar_mufu[h ^ 1][warp & 3]));
+                        ++rounds;
+                    }
                     tc_wait_st();
                     tc_fence_before();
-                    mbar_arrive(smem_u32(&sm.bar_p_full[h]));
+                    mbar_arrive(smem_u32(&sm.bar_p_full[h][buf]));
                 }
                 // epilogue: O / l -> bf16 -> global; O_h is handed back to the issuer as soon as it sits in registers
-                if (ok && n_kept > 0) ok = mbar_wait(smem_u32(&sm.bar_o_full[h]), na & 1, abort_flag, p.status, kErrOFull);
-                if (ok && n_kept > 0) {
+                if (ok) ok = mbar_wait(smem_u32(&sm.bar_o_full[h]), na & 1, abort_flag, p.status, kErrOFull);
+                if (ok) {
                     tc_fence_after();
                     const float inv = l_sum > 0.f ? 1.f / l_sum : 0.f;
                     __nv_bfloat16* orow = p.o + (((size_t)hd.b * p.Hq + hd.head0 + h) * p.N + qi) * D;
@@ -670,13 +692,13 @@ static EncodeTiledFn get_encode_fn() {
     return fn;
 }
 
-// [heads, N, D] bf16 viewed as a 3-D tensor (D innermost); box = 64 x 128 x 1 with 128-byte swizzle; rows past N read zero
-static int make_map(CUtensorMap* map, const void* base, int heads, int N, int D) {
+// [heads, N, D] bf16 viewed as a 3-D tensor (D innermost); box = 64 x box_rows x 1 with 128-byte swizzle; rows past N read zero
+static int make_map(CUtensorMap* map, const void* base, int heads, int N, int D, int box_rows) {
     EncodeTiledFn fn = get_encode_fn();
     if (!fn) return fail(NATS_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
     cuuint64_t dims[3] = {(cuuint64_t)D, (cuuint64_t)N, (cuuint64_t)heads};
     cuuint64_t strides[2] = {(cuuint64_t)D * 2, (cuuint64_t)N * D * 2};
-    cuuint32_t box[3] = {64, 128, 1};
+    cuuint32_t box[3] = {64, (cuuint32_t)box_rows, 1};
     cuuint32_t estr[3] = {1, 1, 1};
     CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -748,9 +770,9 @@ extern "C" __attribute__((visibility("default"))) int nats_b200_prefill_fwd(cons
     int32_t* tmin = (int32_t*)(ws + w.tmin);
     if (int rc = nats_b200_role_prep(d_roles, B, Hkv, N, C, SW, lim, tmax, tmin, d_kept_tiles, stream)) return rc;
     CUtensorMap mq, mk, mv;
-    if (int rc = make_map(&mq, d_q, B * Hq, N, D)) return rc;
-    if (int rc = make_map(&mk, d_k, B * Hkv, N, D)) return rc;
-    if (int rc = make_map(&mv, d_v, B * Hkv, N, D)) return rc;
+    if (int rc = make_map(&mq, d_q, B * Hq, N, D, 128)) return rc;
+    if (int rc = make_map(&mk, d_k, B * Hkv, N, D, kSub)) return rc;
+    if (int rc = make_map(&mv, d_v, B * Hkv, N, D, kSub)) return rc;
     PrefillParams p;
     p.o = (__nv_bfloat16*)d_o; p.lim = lim; p.tile_max = tmax; p.tile_min = tmin; p.status = d_status;
     p.Hq = Hq; p.Hkv = Hkv; p.N = N; p.C = C; p.Nc = cdiv(N, C); p.Nt = cdiv(N, kTile);
@@ -814,4 +836,5 @@ extern "C" __attribute__((visibility("default"))) int nats_b200_prefill_fwd_stat
     return nats_b200_prefill_fwd(d_q, d_k, d_v, d_o, d_roles, B, Hq, Hkv, N, D, C, SW, sm_scale, scratch,
                                  nats::kStaticScratchBytes, d_kept_tiles, d_status, stream);
 }
+
 
