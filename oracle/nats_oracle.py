@@ -215,6 +215,54 @@ class ChunkCacheOracle:
     def decode_mask(self) -> np.ndarray:
         return self.valid[:, :, :self.n_ctx_data + 1]
 
+    # -- mask of a multi-token call over an existing cache -- :444-511, 589-620, 658-713
+    def layout_row_limit(self) -> np.ndarray:
+        """Call after ``update`` of a multi-token continuation.  int64 [B,H,T0/C + Nc_new]: for every chunk of the
+        physical layout ``[ring | kept | gap | unfinished chunk + new tokens]`` the last cache POSITION of a query that
+        may still see it (a query token sits at the position its own K/V was appended to); -1 = never.
+
+        The reference builds the same mask from three pieces: ring slots by their age in the queue
+        (``_fit_sliding_queue_masks`` :658-713: a slot written a chunks before the newest stays visible while the
+        query's chunk is at most SW/C - 1 - a chunks into the new tokens), kept local chunks until the first global chunk of
+        the new tokens (:479-491), kept global chunks always, and the new tokens by the rule of a first call
+        (``_generate_local_mask`` :589-620) -- together: the first-call rule applied to the whole logical sequence."""
+        C, SW = self.C, self.SW
+        W = SW // C
+        t0 = self.n_ctx_data // C * C
+        n_old = t0 // C
+        lim_new = row_limit(self.roles, C, SW)                                  # [B,H,Nc_new], rows counted from t0
+        lim_new = np.where(lim_new >= NO_LIMIT, NO_LIMIT, lim_new + t0)
+        fill = next_global_index(self.roles)[..., 0]                            # first global (or last) new chunk
+        lim_local = t0 + (fill + 1) * C - 1
+        lim = np.full((self.B, self.H, n_old), -1, np.int64)
+        j = np.arange(n_old)
+        sg, sl = self.size_global // C, self.size_local // C
+        lim = np.where((j[None, None] >= W) & (j[None, None] < sg[..., None]), NO_LIMIT, lim)
+        is_loc = (j[None, None] >= sg[..., None]) & (j[None, None] < (sg + sl)[..., None])
+        lim = np.where(is_loc, lim_local[..., None], lim)
+        age = (self.tail // C - 1 - np.arange(W)) % W                            # 0 = newest slot
+        ring_valid = self.valid[:, :, :SW:C]                                     # a slot holds one chunk
+        lim[..., :W] = np.where(ring_valid, t0 + (W - age) * C - 1, -1)
+        return np.concatenate([lim, lim_new], -1)
+
+    def prefill_mask_past(self, x_len: int) -> np.ndarray:
+        """bool [B,H,x_len,n_ctx_data + x_len] of a multi-token call over an existing cache (after ``update``)."""
+        C = self.C
+        L = self.n_ctx_data + x_len
+        lim = np.repeat(self.layout_row_limit(), C, axis=-1)[..., :L]
+        qpos = np.arange(self.n_ctx_data, L, dtype=np.int64)[:, None]
+        k = np.arange(L, dtype=np.int64)[None, :]
+        return (k <= qpos)[None, None] & (qpos[None, None] <= lim[:, :, None, :])
+
+    def prefill_attention_past(self, q: torch.Tensor, x_len: int, sm_scale: float | None = None) -> torch.Tensor:
+        """Attention of the x_len new queries over the cache that ``update`` has just extended
+        (nats_chunk_attention.py:131-142 with the mask of :444-511).  q [B,Hq,x_len,D] -> fp32 [B,Hq,x_len,D]."""
+        L = self.n_ctx_data + x_len
+        mask = torch.from_numpy(self.prefill_mask_past(x_len))
+        k = torch.from_numpy(np.ascontiguousarray(self.cache_k[:, :, :L]))
+        v = torch.from_numpy(np.ascontiguousarray(self.cache_v[:, :, :L]))
+        return masked_attention(q, k, v, mask, sm_scale)
+
     # -- ring fill -- :391-437
     def _ring_fill(self, n_new_chunks: int, n_rem: int, x_len: int):
         C, SW = self.C, self.SW
@@ -309,7 +357,10 @@ class ChunkCacheOracle:
         counts = keep.sum(-1)
         base = np.where(last_g == -1, (self.size_global + self.size_local) // C, self.size_global // C)
         src_base = self.n_ctx_data // C
-        move_tail = n_rem != 0 and counts.max() < Nc - 1            # :840
+        # The reference moves the unfinished chunk only if no head kept every completed chunk of the call (:840); that leaves
+        # it behind when such a head is not the longest one (multi-token call over an existing cache).  Moving it whenever it
+        # exists is the same operation wherever the reference is self-consistent (source == destination there).
+        move_tail = n_rem != 0
         tail_dst = int((counts + base).max())
         for name in ('cache_k', 'cache_v'):
             cache = getattr(self, name)

@@ -45,6 +45,21 @@ CASES = {
     'k64_ragged':     dict(B=2, Hq=4, Hkv=2, N=300, D=64,  C=16,  SW=64,  pg=0.10, pl=0.30, seed=13, n_decode=40),
     'k128_decode':    dict(B=2, Hq=4, Hkv=2, N=256, D=128, C=32,  SW=64,  pg=0.15, pl=0.30, seed=14, n_decode=70),
 }
+# multi-token calls over an existing cache: the sequence is fed in the given segments (N = their sum), then decoded.
+# Shapes avoid two reference defects: a first segment shorter than one chunk followed by a multi-token call raises
+# (nats_chunk_layer_cache.py:676), and a continuation that starts before the window has filled and runs past it hides the
+# ring's chunks in reversed order (:670-679).
+SEG_CASES = {
+    'seg_tiny_aligned':  dict(B=2, Hq=4, Hkv=2, D=16, C=8,  SW=32, segs=[64, 64, 32], pg=0.10, pl=0.30, seed=21, n_decode=20),
+    'seg_tiny_ragged':   dict(B=2, Hq=4, Hkv=2, D=16, C=16, SW=32, segs=[48, 100, 60], pg=0.10, pl=0.30, seed=22, n_decode=20),
+    'seg_tiny_steps':    dict(B=1, Hq=2, Hkv=2, D=16, C=8,  SW=32, segs=[64, 5, 5, 54], pg=0.15, pl=0.30, seed=29, n_decode=12),
+    'seg_tiny_unfilled': dict(B=2, Hq=2, Hkv=2, D=16, C=8,  SW=64, segs=[24, 40, 64], pg=0.10, pl=0.30, seed=24, n_decode=10),
+    'seg_tiny_sparse':   dict(B=1, Hq=2, Hkv=2, D=16, C=4,  SW=16, segs=[30, 30, 30, 30], pg=0.03, pl=0.25, seed=25, n_decode=10),
+    'seg_k64':           dict(B=1, Hq=4, Hkv=2, D=64,  C=64, SW=128, segs=[512, 384, 200], pg=0.10, pl=0.30, seed=26, n_decode=0),
+    'seg_k128':          dict(B=2, Hq=4, Hkv=2, D=128, C=32, SW=64,  segs=[256, 256, 100], pg=0.10, pl=0.30, seed=27, n_decode=40),
+}
+for _c in SEG_CASES.values():
+    _c['N'] = sum(_c['segs'])
 ROW_STRIDE = 5
 
 
@@ -178,14 +193,86 @@ def run_case(name: str, case: dict, NAtSCache, Layer) -> dict:
     return out
 
 
+def segment_roles(case: dict, roles: np.ndarray, pos: int, fill: int, x_len: int) -> np.ndarray:
+    """Role codes a caller passes with a segment: one per chunk from the unfinished chunk on; an unfinished last chunk is
+    marked global (nats_chunk_attention.py:92-94), a call that completes no chunk passes the placeholder (:81-84)."""
+    C = case['C']
+    if fill + x_len < C:
+        return np.zeros(roles.shape[:2] + (1,), np.uint8)
+    r = roles[..., (pos - fill) // C:-(-(pos + x_len) // C)].copy()
+    if (pos + x_len) % C:
+        r[..., -1] = 0
+    return r
+
+
+def run_segmented_case(name: str, case: dict, NAtSCache, Layer) -> dict:
+    from oracle.nats_oracle import onehot_from_roles, make_roles
+    B, Hq, Hkv, N, D, C, SW = (case[x] for x in ('B', 'Hq', 'Hkv', 'N', 'D', 'C', 'SW'))
+    roles = make_roles(B, Hkv, -(-N // C), case['pg'], case['pl'], case['seed'], force_first_global=True)
+    q, k, v, steps = golden_inputs(case)
+    layer = Layer(dim=Hq * D, n_heads=Hq, n_kv_heads=Hkv, layer_id=0, local_seq_max_length=SW, chunk_size=C)
+    layer.eval()
+    cache = NAtSCache(sliding_window_size=SW, chunk_size=C)
+    out = {'roles': roles, 'in_checksum': checksum(q, k, v), 'segs': np.array(case['segs'])}
+    tiny = D < 64
+    pos = 0
+    with torch.no_grad():
+        for si, x_len in enumerate(case['segs']):
+            fill = cache.get_nats_chunk_fill_size(0)
+            r = segment_roles(case, roles, pos, fill, x_len)
+            info = {'token_states_info': onehot_from_roles(r)}
+            qs, ks, vs = (t[:, :, pos:pos + x_len] for t in (q, k, v))
+            keys, values = layer.prepare_kv(qs, ks, vs, pos, cache=cache, kwargs=info)
+            mask = cache.generate_mask(0, x_len).numpy().copy()
+            keys, values = layer.repeat_kv_values(keys, values)
+            o = layer.multi_head_attention(qs, keys, values, cache=cache, kwargs=info)
+            lc = cache.cache_model[0]
+            out[f's{si}_out'] = o.numpy() if tiny else o[:, :, ::ROW_STRIDE].numpy()
+            out[f's{si}_mask'] = np.packbits(mask if tiny else mask[:, :, ::ROW_STRIDE], axis=-1)
+            out[f's{si}_mask_cols'] = np.int64(mask.shape[-1])
+            for key, val in state_of(lc).items():
+                if tiny or key not in ('cache_k', 'cache_v'):
+                    out[f's{si}_{key}'] = val
+            pos += x_len
+        dec_out, dec_nctx, dec_sizes = [], [], []
+        fill = int(lc.chunk_fill_size)
+        for (q1, k1, v1, r1) in steps:
+            fill += 1
+            done = fill == C
+            role_now = r1 if done else np.zeros_like(r1)
+            if done:
+                fill = 0
+            info1 = {'token_states_info': onehot_from_roles(role_now[..., None])}
+            keys, values = layer.prepare_kv(q1, k1, v1, 0, cache=cache, kwargs=info1)
+            keys, values = layer.repeat_kv_values(keys, values)
+            o1 = layer.multi_head_attention(q1, keys, values, cache=cache, kwargs=info1)
+            dec_out.append(o1.numpy().copy())
+            dec_nctx.append(int(lc.n_ctx_data))
+            dec_sizes.append(np.stack([lc.size_global_kv.numpy().copy(), lc.size_local_kv.numpy().copy()]))
+        if steps:
+            out['dec_out'] = np.stack(dec_out)
+            out['dec_nctx'] = np.array(dec_nctx)
+            out['dec_sizes'] = np.stack(dec_sizes)
+            out['dec_roles'] = np.stack([s[3] for s in steps])
+            out['dec_checksum'] = np.array([checksum(*s[:3]) for s in steps])
+            for key, val in state_of(lc).items():
+                if tiny or key not in ('cache_k', 'cache_v'):
+                    out['post_' + key] = val
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument('--reference', required=True)
+    ap.add_argument('--only', default='', help='comma-separated case names (default: all)')
     args = ap.parse_args()
     sys.path.insert(0, os.path.join(HERE, '..', '..'))
     NAtSCache, Layer = load_reference(args.reference)
-    for name, case in CASES.items():
-        res = run_case(name, case, NAtSCache, Layer)
+    only = set(filter(None, args.only.split(',')))
+    for name, case in list(CASES.items()) + list(SEG_CASES.items()):
+        if only and name not in only:
+            continue
+        res = (run_segmented_case if name in SEG_CASES else run_case)(name, case, NAtSCache, Layer)
         path = os.path.join(HERE, name + '.npz')
         np.savez_compressed(path, **res)
         print(f'{name}: {os.path.getsize(path) / 1024:.1f} KiB')

@@ -3,7 +3,7 @@ import numpy as np
 import pytest
 import torch
 
-from golden_util import CASES, ROW_STRIDE, load
+from golden_util import CASES, ROW_STRIDE, SEG_CASES, load, segment_roles
 from oracle import nats_oracle as orc
 
 TINY = [n for n, c in CASES.items() if c['D'] < 64]
@@ -117,3 +117,72 @@ def test_decode_equals_one_shot_prefill():
         o = torch.einsum('bgrl,bgld->bgrd', torch.softmax(s1, -1), vv).reshape(B, Hq, D)
         st.post_update(1)
         assert (o - full[:, :, t]).abs().max() < 1e-12, i
+
+
+# ---- multi-token calls over an existing cache (segmented prefill) ----------------------------------------------------
+def run_oracle_segments(case, roles, q, k, v, on_segment=None):
+    """Feeds the sequence to the oracle in the case's segments; on_segment(si, state, mask_or_None, out) after each."""
+    st = orc.ChunkCacheOracle(case['B'], case['Hkv'], case['SW'], case['C'])
+    pos = 0
+    for si, x_len in enumerate(case['segs']):
+        r = segment_roles(case, roles, pos, st.chunk_fill, x_len)
+        qs, ks, vs = (t[:, :, pos:pos + x_len] for t in (q, k, v))
+        st.update(ks.numpy(), vs.numpy(), r)
+        if si == 0:
+            mask = orc.visible_mask(r, case['C'], case['SW'], x_len)
+            out = orc.prefill_attention(qs, ks, vs, r, case['C'], case['SW'])
+        else:
+            mask = st.prefill_mask_past(x_len)
+            out = st.prefill_attention_past(qs, x_len)
+        st.post_update(x_len)
+        if on_segment is not None:
+            on_segment(si, st, mask, out)
+        pos += x_len
+    return st
+
+
+@pytest.mark.parametrize('name', list(SEG_CASES))
+def test_segmented_prefill_matches_reference(name):
+    case, fx, (q, k, v, _) = load(name)
+    tiny = case['D'] < 64
+
+    def check(si, st, mask, out):
+        cols = int(fx[f's{si}_mask_cols'])
+        ref_mask = np.unpackbits(fx[f's{si}_mask'], axis=-1)[..., :cols].astype(bool)
+        got_mask = mask if tiny else mask[:, :, ::ROW_STRIDE]
+        assert got_mask.shape == ref_mask.shape
+        assert np.array_equal(got_mask, ref_mask), f'segment {si}'
+        got = out.numpy() if tiny else out[:, :, ::ROW_STRIDE].numpy()
+        np.testing.assert_allclose(got, fx[f's{si}_out'], rtol=1e-4, atol=2e-5, err_msg=f'segment {si}')
+        _check_state(st, fx, f's{si}_', full=tiny)
+
+    run_oracle_segments(case, fx['roles'], q, k, v, check)
+
+
+@pytest.mark.parametrize('name', list(SEG_CASES))
+def test_segmented_prefill_equals_one_shot(name):
+    """The identity that defines a multi-token call over a cache: the outputs are those of one call over everything."""
+    case, fx, (q, k, v, _) = load(name)
+    outs = []
+    run_oracle_segments(case, fx['roles'], q, k, v, lambda si, st, m, o: outs.append(o))
+    roles = fx['roles'].copy()
+    if case['N'] % case['C']:
+        roles[..., -1] = 0
+    one = orc.prefill_attention(q, k, v, roles, case['C'], case['SW'])
+    np.testing.assert_allclose(torch.cat(outs, 2).numpy(), one.numpy(), rtol=1e-4, atol=2e-5)
+
+
+@pytest.mark.parametrize('name', [n for n, c in SEG_CASES.items() if c['n_decode'] > 0])
+def test_decode_after_segments_matches_reference(name):
+    case, fx, (q, k, v, steps) = load(name)
+    st = run_oracle_segments(case, fx['roles'], q, k, v)
+    C = case['C']
+    for i, (q1, k1, v1, r1) in enumerate(steps):
+        done = st.chunk_fill + 1 == C
+        role_now = (r1 if done else np.zeros_like(r1))[..., None]
+        st.update(k1.numpy(), v1.numpy(), role_now)
+        o = orc.decode_attention(q1, st.cache_k, st.cache_v, st.decode_mask())
+        st.post_update(1)
+        np.testing.assert_allclose(o.numpy(), fx['dec_out'][i], rtol=1e-4, atol=2e-5, err_msg=f'step {i}')
+        assert np.array_equal(np.stack([st.size_global, st.size_local]), fx['dec_sizes'][i]), f'step {i}'
+    _check_state(st, fx, 'post_', full=False)
