@@ -128,6 +128,74 @@ int nats_b200_evict_compact(const void* d_k, const void* d_v, const uint8_t* d_r
                             void* d_cache_k, void* d_cache_v, uint8_t* d_valid, int Lcap, void* stream);
 
 /* ------------------------------------------------------------------------------------------------
+ * Multi-token call over an existing compacted cache (segmented prefill, a further turn of a conversation).
+ *
+ * The reference handles it in NAtSChunkLayerCache.update (:239-256: the new K/V are written behind the unfinished chunk),
+ * _generate_mask with _seen_tokens > 0 (:444-511, with _fit_sliding_queue_masks :658-713), its Triton twin nats_prefill
+ * with HAS_PAST_INFO (src/nats/models/transformer/triton/nats_flashattn_fwd.py:164-380, 693-722), and the general branch of
+ * _post_update (:331-385).  Semantics: the outputs equal those of ONE call over the whole sequence; evicted tokens
+ * are exactly the ones no later query may see.
+ *
+ * Cache layout on entry, per (b,h): [ring SW | kept global [SW,size_global) | kept local [..,len) | gap up to t0 |
+ * unfinished chunk [t0, t0+fill)], t0 = d_state[0] (a multiple of C), same for all heads; capacity = rows per head.
+ *
+ * Step 0 -- append the x_len new tokens at rows [pos, pos+x_len), pos = t0 + fill, and mark them valid.
+ */
+int nats_b200_cache_append(const void* d_k_new, const void* d_v_new, void* d_cache_k, void* d_cache_v, uint8_t* d_valid,
+                           int B, int Hkv, int x_len, int D, int Lcap, int pos, void* stream);
+
+/* Role metadata of such a call (what nats_b200_role_prep is to a first call), over the physical layout as KV sequence of
+ * n_kv = t0 + fill + x_len rows; query row i sits at position t0 + fill + i.
+ *   d_roles_new  uint8 [B,Hkv,ceil((fill+x_len)/C)]: roles of the chunks from the unfinished one on (what the reference
+ *                passes as token_states_info; an unfinished last chunk is marked global by the caller)
+ *   d_valid      uint8, valid_stride bytes per (b,h); only the ring flags [0,SW) of each are read
+ *   tail         ring write position (sliding_queue_tail) before this call
+ *   d_lim int32 [B,Hkv,ceil(n_kv/C)], d_tile_max / d_tile_min int32 [B,Hkv,ceil(n_kv/128)], d_kept_tiles int64 [B,Hkv] or NULL
+ */
+int nats_b200_role_prep_past(const uint8_t* d_roles_new, const uint8_t* d_valid, const int64_t* d_size_global,
+                             const int64_t* d_size_local, int B, int Hkv, int x_len, int C, int SW, int valid_stride,
+                             int t0, int fill, int tail, int32_t* d_lim, int32_t* d_tile_max, int32_t* d_tile_min,
+                             int64_t* d_kept_tiles, void* stream);
+
+size_t nats_b200_prefill_past_workspace_bytes(int B, int Hkv, int n_kv, int C);
+
+/* Step 1 -- attention of the new queries over cache + new tokens (the new tokens already appended by step 0).
+ *   d_q [B,Hq,x_len,D], d_o [B,Hq,x_len,D]; d_cache_k/v [B,Hkv,cache_capacity,D]; the other arguments as above;
+ *   d_workspace: nats_b200_prefill_past_workspace_bytes(B,Hkv,t0+fill+x_len,C) bytes; d_status as in nats_b200_prefill_fwd.
+ *   Rows of the gap [len, t0) must hold finite numbers (this library keeps them zero).
+ */
+int nats_b200_prefill_past_fwd(const void* d_q, const void* d_cache_k, const void* d_cache_v, void* d_o,
+                               const uint8_t* d_roles_new, const uint8_t* d_valid, int valid_stride,
+                               const int64_t* d_size_global, const int64_t* d_size_local, int B, int Hq, int Hkv, int x_len, int D, int C, int SW,
+                               int cache_capacity, int t0, int fill, int tail, float sm_scale,
+                               void* d_workspace, size_t workspace_bytes, int64_t* d_kept_tiles, int32_t* d_status,
+                               void* stream);
+
+/* Step 2 -- keep-set of the call's n_tokens = fill + x_len tokens (get_updated_cache_info :715-868 with a non-empty cache).
+ * A global chunk among the completed chunks drops the kept locals in front of it.
+ *   d_rank int32 [B,Hkv,ceil(n_tokens/C)] (out): destination slot of a kept chunk counted from d_base, or -1
+ *   d_base int32 [B,Hkv] (out): chunk slot (position / C) the first kept chunk goes to = what the cache keeps from before
+ *   d_size_global / d_size_local (in/out);  d_state as in nats_b200_evict_plan
+ */
+int nats_b200_evict_plan_past(const uint8_t* d_roles_new, int B, int Hkv, int n_tokens, int C, int SW,
+                              int32_t* d_rank, int32_t* d_base, int64_t* d_size_global, int64_t* d_size_local,
+                              int32_t* d_state, void* stream);
+
+/* Step 3 -- data movement, out of place: old cache (with the appended tokens) -> new cache buffer.  Ring slots behind
+ * tail_old receive the last min(#completed chunks, SW/C) chunks (move_sliding_window_tokens_to_head :391-437), the
+ * others are copied; [SW, base*C) is copied; kept chunks go to [base*C, len); the new unfinished chunk to
+ * [T0', T0'+r), T0' = d_state[0]; everything else up to Lcap is zero; flags accordingly.  (The reference moves chunks
+ * inside one buffer after cloning the sources, cache_update.py:65-74.)
+ *   t0_old: tail offset before the call (the tokens of the call sit at old rows [t0_old, t0_old + n_tokens))
+ *   Lcap >= ceil((T0' + r)/C)*C
+ */
+int nats_b200_evict_compact_past(const void* d_old_k, const void* d_old_v, const uint8_t* d_old_valid, int old_capacity,
+                                 const uint8_t* d_roles_new, const int32_t* d_rank, const int32_t* d_base,
+                                 const int64_t* d_size_global, const int64_t* d_size_local, const int32_t* d_state,
+                                 int B, int Hkv, int n_tokens, int D, int C, int SW, int t0_old, int tail_old,
+                                 void* d_cache_k, void* d_cache_v, uint8_t* d_valid, int Lcap, void* stream);
+
+/* ------------------------------------------------------------------------------------------------
  * Decode over the compacted ragged cache.
  *
  * Logical sequence a query of (b,h) attends to (the reference's ``valid_tokens[:, :, :n_ctx_data+1]``,

@@ -23,6 +23,14 @@ SIGNATURES = {
     'nats_b200_prefill_fwd_static': (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _P, _P, _P]),
     'nats_b200_evict_plan': (_I, [_P, _I, _I, _I, _I, _I, _P, _P, _P, _P, _P]),
     'nats_b200_evict_compact': (_I, [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P, _P, _P, _I, _P]),
+    'nats_b200_cache_append': (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P]),
+    'nats_b200_role_prep_past': (_I, [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P, _P, _P, _P]),
+    'nats_b200_prefill_past_workspace_bytes': (_SZ, [_I, _I, _I, _I]),
+    'nats_b200_prefill_past_fwd': (_I, [_P, _P, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F,
+                                        _P, _SZ, _P, _P, _P]),
+    'nats_b200_evict_plan_past': (_I, [_P, _I, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P]),
+    'nats_b200_evict_compact_past': (_I, [_P, _P, _P, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I,
+                                          _P, _P, _P, _I, _P]),
     'nats_b200_decode_workspace_bytes': (_SZ, [_I, _I, _I, _I, _I]),
     'nats_b200_decode_fwd': (_I, [_P, _P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _P, _SZ, _P]),
     'nats_b200_decode_place': (_I, [_P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P]),

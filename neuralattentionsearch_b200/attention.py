@@ -138,7 +138,7 @@ class BaseNAtSChunkAttentionLayer(nn.Module):
         elif x_len == 1:
             output = layer_cache.decode_attention(xq, self.sm_scale)
         else:
-            raise NotImplementedError('prefill continuation over an existing compacted cache is not built yet')
+            output = layer_cache.prefill_attention(xq, self.sm_scale)
         if self.executor is not None:
             self._cache_is_till_updating = self.executor.submit(cache.post_update, layer_idx=self.layer_id, x_len=x_len)
         else:

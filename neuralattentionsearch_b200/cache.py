@@ -146,10 +146,16 @@ class NAtSChunkLayerCache:
         if self._buf_k is None and self._pending is None:
             self._pending = (key_states, value_states)
             return key_states, value_states
-        if x_len != 1:
-            raise NotImplementedError('prefill continuation over an existing compacted cache is not built yet')
         kb = key_states.to(torch.bfloat16).contiguous()
         vb = value_states.to(torch.bfloat16).contiguous()
+        if x_len != 1:
+            # several tokens over an existing cache: they are appended behind the unfinished chunk, as the reference does
+            # (:239-256); ``prefill_attention`` then attends over the buffer and ``post_update`` compacts it
+            pos = self.n_ctx_data
+            self._grow(pos + x_len)
+            F_.cache_append(kb, vb, self._buf_k, self._buf_v, self._buf_valid, pos)
+            self._pending = None
+            return self._buf_k[:, :, :pos + x_len], self._buf_v[:, :, :pos + x_len]
         self._pending = (kb, vb)
         if fused:
             return kb, vb
@@ -168,8 +174,27 @@ class NAtSChunkLayerCache:
             n = self.n_ctx_data + 1
             return self._buf_valid[:, :, :n].view(torch.bool).unsqueeze(-2)
         if self._seen_tokens != 0:
-            raise NotImplementedError('prefill continuation over an existing compacted cache is not built yet')
+            n_ctx = self.n_ctx_data
+            t0 = n_ctx // self.chunk_size * self.chunk_size
+            lim = F_.layout_row_limits(self._roles, self._buf_valid, self.size_global_kv, self.size_local_kv, x_len, t0,
+                                       n_ctx - t0, self.sliding_queue_tail, self.chunk_size, self.sliding_window_size)
+            L = n_ctx + x_len
+            lim_tok = lim.repeat_interleave(self.chunk_size, -1)[..., :L].long()
+            qpos = torch.arange(n_ctx, L, device=self.device)
+            kpos = torch.arange(L, device=self.device)
+            return (kpos[None, :] <= qpos[:, None])[None, None] & (qpos[None, None, :, None] <= lim_tok[:, :, None, :])
         return F_.dense_role_mask(self._roles, self.chunk_size, self.sliding_window_size, x_len)
+
+    def prefill_attention(self, xq: torch.Tensor, sm_scale: float | None = None,
+                          kept_tiles: torch.Tensor | None = None) -> torch.Tensor:
+        """Attention of several new tokens over the existing cache; ``update`` must have appended their K/V.
+        xq [B,Hq,x_len,D] -> [B,Hq,x_len,D].  The outputs are those one call over the whole sequence would give."""
+        x_len = xq.shape[2]
+        n_ctx = self.n_ctx_data
+        t0 = n_ctx // self.chunk_size * self.chunk_size
+        return F_.prefill_attention_past(xq, self._buf_k, self._buf_v, self._buf_valid, self._roles, self.size_global_kv,
+                                         self.size_local_kv, t0, n_ctx - t0, self.sliding_queue_tail, self.chunk_size,
+                                         self.sliding_window_size, sm_scale, kept_tiles)
 
     def decode_attention(self, xq: torch.Tensor, sm_scale: float | None = None) -> torch.Tensor:
         """Attention of one new token per sequence over the compacted cache, fused with its append.
@@ -202,8 +227,11 @@ class NAtSChunkLayerCache:
         if self.chunk_fill_size < C:
             self.chunk_fill_size_last = self.chunk_fill_size
             return
+        if x_len != 1:
+            self._evict_after_continuation()
+            return
         # a chunk has just been completed by single-token steps: ring write + placement
-        assert x_len == 1 and self._roles is not None
+        assert self._roles is not None
         roles = self._roles.reshape(self.bsz, self.n_msks, -1)[..., 0].contiguous()
         F_.decode_place(roles, self._buf_k, self._buf_v, self._buf_valid, self.size_global_kv, self.size_local_kv,
                         self._state, self.sliding_queue_tail, C, SW)
@@ -215,6 +243,31 @@ class NAtSChunkLayerCache:
         self._pending = None
         if self._t0_bound - self._t0_synced >= 8 * C:
             self._t0()        # the bound drifts up when chunks are dropped: refresh it now and then (one small read)
+
+    def _evict_after_continuation(self):
+        """Compaction after a multi-token call over an existing cache (reference: the general branch of _post_update,
+        :331-385).  Out of place: the old buffer, which holds the call's tokens behind the old tail offset, is the source."""
+        C, SW = self.chunk_size, self.sliding_window_size
+        n_tokens = self.chunk_fill_size                           # unfinished chunk before the call + the new tokens
+        n_full, rem = divmod(n_tokens, C)
+        B, H, _, D = self._buf_k.shape
+        roles = self._roles
+        if roles is None or roles.shape != (B, H, -(-n_tokens // C)):
+            raise ValueError(f'token_states_info must describe {-(-n_tokens // C)} chunks')
+        t0_old = self._t0()
+        rank = torch.empty(B, H, roles.shape[-1], dtype=torch.int32, device=self.device)
+        base = torch.empty(B, H, dtype=torch.int32, device=self.device)
+        F_.evict_plan_past(roles, n_tokens, C, SW, rank, base, self.size_global_kv, self.size_local_kv, self._state)
+        self._t0_exact = None
+        t0 = self._t0()                                           # the one host read of the call
+        old = (self._buf_k, self._buf_v, self._buf_valid)
+        self._alloc(math.ceil((t0 + rem) / C) * C + self.headroom, D)
+        F_.evict_compact_past(*old, roles, rank, base, self.size_global_kv, self.size_local_kv, self._state, n_tokens, C, SW,
+                              t0_old, self.sliding_queue_tail, self._buf_k, self._buf_v, self._buf_valid)
+        self.sliding_queue_tail = (self.sliding_queue_tail + min(n_full, self.n_chunks_per_sw) * C) % SW
+        self.chunk_fill_size = rem
+        self.chunk_fill_size_last = rem
+        self._pending = None
 
     def _evict_after_prefill(self, x_len: int):
         C, SW = self.chunk_size, self.sliding_window_size

@@ -23,21 +23,14 @@ constexpr int kScanThreads = 256;
 // =================================================================================================
 // role_prep: per-chunk row limit, per-tile max/min limit, kept-tile count
 // =================================================================================================
-__global__ void __launch_bounds__(kScanThreads)
-role_prep_kernel(const uint8_t* __restrict__ roles, int Nc, int N, int C, int SW, int Nt,
-                 int32_t* __restrict__ lim, int32_t* __restrict__ tmax, int32_t* __restrict__ tmin,
-                 long long* __restrict__ kept) {
-    const int bh = blockIdx.x, tid = threadIdx.x;
-    roles += (size_t)bh * Nc;
-    lim += (size_t)bh * Nc;
-    tmax += (size_t)bh * Nt;
-    tmin += (size_t)bh * Nt;
-    __shared__ int s[kScanThreads];
-    __shared__ int carry;
-    __shared__ unsigned long long kept_sm;
-    if (tid == 0) { carry = Nc - 1; kept_sm = 0; }   // the last chunk counts as global for the next-global index
+// Row limits of Nc chunks whose first token sits at position pos0: lim[c] = last query position that may see chunk c.
+// Next-global index by a reversed inclusive min-scan, 256 chunks at a time from the end of the sequence; the last chunk
+// counts as global.  *first_gf receives the index of the first global (or last) chunk.  All threads of the block call.
+__device__ void scan_role_limits(const uint8_t* __restrict__ roles, int Nc, int C, int SW, int pos0,
+                                 int32_t* __restrict__ lim, int* s, int* carry, int* first_gf) {
+    const int tid = threadIdx.x;
+    if (tid == 0) *carry = Nc - 1;
     __syncthreads();
-    // next-global index by a reversed inclusive min-scan, 256 chunks at a time from the end of the sequence
     for (int hi = Nc; hi > 0; hi -= kScanThreads) {
         const int c = hi - 1 - tid;
         const int role = (c >= 0) ? roles[c] : NATS_ROLE_LOCAL;
@@ -50,27 +43,29 @@ role_prep_kernel(const uint8_t* __restrict__ roles, int Nc, int N, int C, int SW
             s[tid] = min(s[tid], v);
             __syncthreads();
         }
-        const int fill = min(s[tid], carry);
+        const int fill = min(s[tid], *carry);
         if (c >= 0) {
-            int l;
-            if (role == NATS_ROLE_SLIDING) {
-                l = (int)min((long long)c * C + SW + C - 1, (long long)kNoLimit);
-            } else if (gf) {
-                l = kNoLimit;
-            } else {
-                l = (int)min(((long long)fill + 1) * C - 1, (long long)kNoLimit);
-            }
-            lim[c] = l;
+            long long l;
+            if (role == NATS_ROLE_SLIDING) l = (long long)pos0 + (long long)c * C + SW + C - 1;
+            else if (gf) l = kNoLimit;
+            else l = (long long)pos0 + ((long long)fill + 1) * C - 1;
+            lim[c] = (int)min(l, (long long)kNoLimit);
+            if (c == 0) *first_gf = fill;
         }
         __syncthreads();
-        if (tid == kScanThreads - 1) carry = fill;
+        if (tid == kScanThreads - 1) *carry = fill;
         __syncthreads();
     }
-    // per 128-column tile: max / min of the limits of the chunks it overlaps, and how many q tiles keep it
+}
+
+// Per 128-row KV tile: max / min of the limits of the chunks it overlaps, and how many query tiles keep it.  Query row i
+// sits at position q_off + i; there are Nt query tiles of 128 rows.  Returns this thread's share of the kept count.
+__device__ unsigned long long tile_limits(const int32_t* __restrict__ lim, int Nkv, int C, int Ntk, int q_off, int Nt,
+                                          int32_t* __restrict__ tmax, int32_t* __restrict__ tmin) {
     unsigned long long mine = 0;
-    for (int kt = tid; kt < Nt; kt += kScanThreads) {
+    for (int kt = threadIdx.x; kt < Ntk; kt += kScanThreads) {
         const int c0 = (int)(((long long)kt * kTile) / C);
-        const int c1 = (int)(min((long long)kt * kTile + kTile - 1, (long long)N - 1) / C);
+        const int c1 = (int)(min((long long)kt * kTile + kTile - 1, (long long)Nkv - 1) / C);
         int mx = -1, mn = kNoLimit;
         for (int c = c0; c <= c1; ++c) {
             const int l = lim[c];
@@ -79,13 +74,86 @@ role_prep_kernel(const uint8_t* __restrict__ roles, int Nc, int N, int C, int SW
         }
         tmax[kt] = mx;
         tmin[kt] = mn;
-        const int last_t = min(Nt - 1, mx / kTile);
-        if (last_t >= kt) mine += (unsigned long long)(last_t - kt + 1);
+        // query tiles t that keep the tile: last row position >= first tile row, first row position <= mx
+        const long long first = (long long)kt * kTile - q_off - (kTile - 1);
+        const int t_min = first <= 0 ? 0 : (int)((first + kTile - 1) / kTile);
+        if (mx >= q_off) {
+            const int t_max = min(Nt - 1, (mx - q_off) / kTile);
+            if (t_max >= t_min) mine += (unsigned long long)(t_max - t_min + 1);
+        }
     }
+    return mine;
+}
+
+__global__ void __launch_bounds__(kScanThreads)
+role_prep_kernel(const uint8_t* __restrict__ roles, int Nc, int N, int C, int SW, int Nt,
+                 int32_t* __restrict__ lim, int32_t* __restrict__ tmax, int32_t* __restrict__ tmin,
+                 long long* __restrict__ kept) {
+    const int bh = blockIdx.x, tid = threadIdx.x;
+    roles += (size_t)bh * Nc;
+    lim += (size_t)bh * Nc;
+    tmax += (size_t)bh * Nt;
+    tmin += (size_t)bh * Nt;
+    __shared__ int s[kScanThreads];
+    __shared__ int carry, first_gf;
+    __shared__ unsigned long long kept_sm;
+    if (tid == 0) kept_sm = 0;
+    scan_role_limits(roles, Nc, C, SW, 0, lim, s, &carry, &first_gf);
+    const unsigned long long mine = tile_limits(lim, N, C, Nt, 0, Nt, tmax, tmin);
     if (kept != nullptr) {
         atomicAdd(&kept_sm, mine);
         __syncthreads();
         if (tid == 0) kept[bh] = (long long)kept_sm;
+    }
+}
+
+// The same metadata for a multi-token call over an existing cache.  The KV sequence is the physical cache layout
+// [ring | kept global | kept local | gap | unfinished chunk + new tokens]; T0 = first position of the unfinished chunk.
+struct PastPrepParams {
+    const uint8_t* roles;                       // [BH, Ncn] roles of the chunks from the unfinished one on
+    const uint8_t* valid;                       // [BH, Lcap]; only the ring flags [0, SW) of a head are read
+    const long long* size_global; const long long* size_local;
+    int32_t* lim; int32_t* tmax; int32_t* tmin; long long* kept;
+    int Ncn, Lcap, T0, C, SW, tail, Nq, q_off, Nkv, Nc, Ntk, Nt;
+};
+
+__global__ void __launch_bounds__(kScanThreads) role_prep_past_kernel(const PastPrepParams p) {
+    const int bh = blockIdx.x, tid = threadIdx.x;
+    const uint8_t* roles = p.roles + (size_t)bh * p.Ncn;
+    const uint8_t* valid = p.valid + (size_t)bh * p.Lcap;
+    int32_t* lim = p.lim + (size_t)bh * p.Nc;
+    __shared__ int s[kScanThreads];
+    __shared__ int carry, first_gf;
+    __shared__ unsigned long long kept_sm;
+    if (tid == 0) kept_sm = 0;
+    const int n_old = p.T0 / p.C, W = p.SW / p.C;
+    // new chunks: the rule of a first call, positions counted from T0
+    scan_role_limits(roles, p.Ncn, p.C, p.SW, p.T0, lim + n_old, s, &carry, &first_gf);
+    // cached chunks
+    const int sg = (int)(p.size_global[bh] / p.C), sl = (int)(p.size_local[bh] / p.C);
+    const long long lim_local = (long long)p.T0 + ((long long)first_gf + 1) * p.C - 1;   // until the first new global chunk ends
+    for (int j = tid; j < n_old; j += kScanThreads) {
+        int l;
+        if (j < W) {
+            // ring slot j was written `age` chunks before the newest one; a sliding chunk is seen by the SW/C chunks after it
+            const int age = ((p.tail / p.C - 1 - j) % W + W) % W;
+            l = valid[(size_t)j * p.C] ? p.T0 + (W - age) * p.C - 1 : -1;
+        } else if (j < sg) {
+            l = kNoLimit;
+        } else if (j < sg + sl) {
+            l = (int)min(lim_local, (long long)kNoLimit);
+        } else {
+            l = -1;                                   // between this head's length and the longest head's
+        }
+        lim[j] = l;
+    }
+    __syncthreads();
+    const unsigned long long mine = tile_limits(lim, p.Nkv, p.C, p.Ntk, p.q_off, p.Nt,
+                                                p.tmax + (size_t)bh * p.Ntk, p.tmin + (size_t)bh * p.Ntk);
+    if (p.kept != nullptr) {
+        atomicAdd(&kept_sm, mine);
+        __syncthreads();
+        if (tid == 0) p.kept[bh] = (long long)kept_sm;
     }
 }
 
@@ -110,10 +178,13 @@ __device__ __forceinline__ void publish_max_len(int32_t* state, int len, int nbl
     }
 }
 
+// base == nullptr: first call (the cache is empty: sizes are outputs).  Otherwise the sizes are read and updated, and
+// base[bh] receives the chunk slot (counted from position 0) the first kept chunk of this call goes to: behind the
+// kept locals if the call brings no global chunk, else behind the kept globals (the locals in front of it are dropped).
 __global__ void __launch_bounds__(kScanThreads)
 evict_plan_kernel(const uint8_t* __restrict__ roles, int Nc, int n_full, int C, int SW,
                   int32_t* __restrict__ rank, long long* __restrict__ size_global,
-                  long long* __restrict__ size_local, int32_t* __restrict__ state) {
+                  long long* __restrict__ size_local, int32_t* __restrict__ state, int32_t* __restrict__ base) {
     const int bh = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     roles += (size_t)bh * Nc;
     rank += (size_t)bh * Nc;
@@ -153,11 +224,14 @@ evict_plan_kernel(const uint8_t* __restrict__ roles, int Nc, int n_full, int C, 
         __syncthreads();
     }
     const int n_kept = s_base, n_g = s_ng;
-    const long long sg = (long long)SW + (long long)C * n_g;
-    const long long sl = (long long)C * (n_kept - n_g);
+    long long sg0 = SW, sl0 = 0;
+    if (base != nullptr) { sg0 = size_global[bh]; sl0 = size_local[bh]; }
+    const long long sg = sg0 + (long long)C * n_g;
+    const long long sl = (last_g >= 0 ? 0 : sl0) + (long long)C * (n_kept - n_g);
     if (tid == 0) {
         size_global[bh] = sg;
         size_local[bh] = sl;
+        if (base != nullptr) base[bh] = (int)((last_g >= 0 ? sg0 : sg0 + sl0) / C);
     }
     publish_max_len(state, (int)(sg + sl), gridDim.x);
 }
@@ -169,11 +243,16 @@ constexpr int kCopyThreads = 256;
 constexpr int kTokPerBlock = 64;
 
 struct CompactParams {
-    const uint8_t* k; const uint8_t* v;          // [BH, N, rowB] bytes
+    // source of the tokens of this call: [BH, src_stride, rowB] bytes; token t of the call sits at row src_off + t.
+    // First call: the caller's K/V (src_off 0).  Call over an existing cache: the old cache buffer, to which the new
+    // tokens were appended behind the unfinished chunk (src_off = old T0); it also holds the old ring and kept region.
+    const uint8_t* k; const uint8_t* v; const uint8_t* old_valid;
     const uint8_t* roles; const int32_t* rank;   // [BH, Nc]
+    const int32_t* base;                         // [BH] or nullptr (first call: SW / C)
     const long long* size_global; const long long* size_local; const int32_t* state;
     uint8_t* ck; uint8_t* cv; uint8_t* valid;    // [BH, Lcap, rowB], [BH, Lcap]
-    int N, Nc, n_full, C, SW, Lcap, rowB;        // rowB = D * 2 bytes
+    long long src_stride;                        // rows per head of the source
+    int src_off, tail, N, Nc, n_full, C, SW, Lcap, rowB;        // rowB = D * 2 bytes; N = tokens of the call
     int nA, nB;                                  // blocks in sections A (source tokens) and B (ring)
 };
 
@@ -182,14 +261,15 @@ __global__ void __launch_bounds__(kCopyThreads) evict_compact_kernel(const Compa
     const int vpt = p.rowB >> 4;                          // 16-byte vectors per token row
     const int tpp = kCopyThreads / vpt;                   // tokens per pass
     const int trow = tid / vpt, tvec = (tid % vpt) << 4;
-    const uint8_t* k = p.k + (size_t)bh * p.N * p.rowB;
-    const uint8_t* v = p.v + (size_t)bh * p.N * p.rowB;
+    const uint8_t* k = p.k + (size_t)bh * p.src_stride * p.rowB;
+    const uint8_t* v = p.v + (size_t)bh * p.src_stride * p.rowB;
     uint8_t* ck = p.ck + (size_t)bh * p.Lcap * p.rowB;
     uint8_t* cv = p.cv + (size_t)bh * p.Lcap * p.rowB;
     uint8_t* valid = p.valid + (size_t)bh * p.Lcap;
     const uint8_t* roles = p.roles + (size_t)bh * p.Nc;
     const int32_t* rank = p.rank + (size_t)bh * p.Nc;
-    const int base = p.SW / p.C;                          // first chunk slot behind the ring
+    const bool past = p.base != nullptr;
+    const int base = past ? p.base[bh] : p.SW / p.C;      // chunk slot of the first kept chunk of this call
     const uint4 zero = make_uint4(0, 0, 0, 0);
     int blk = blockIdx.x;
     if (trow >= tpp) return;                              // head dims whose vector count does not divide 256
@@ -203,7 +283,7 @@ __global__ void __launch_bounds__(kCopyThreads) evict_compact_kernel(const Compa
             const int r = rank[c];
             if (r < 0) continue;
             const size_t dst = ((size_t)(base + r) * p.C + (t - c * p.C)) * p.rowB + tvec;
-            const size_t src = (size_t)t * p.rowB + tvec;
+            const size_t src = (size_t)(p.src_off + t) * p.rowB + tvec;
             st16(ck + dst, ld16_stream(k + src));
             st16(cv + dst, ld16_stream(v + src));
         }
@@ -211,7 +291,8 @@ __global__ void __launch_bounds__(kCopyThreads) evict_compact_kernel(const Compa
     }
     blk -= p.nA;
     if (blk < p.nB) {
-        // section B: the ring holds the last min(n_full, SW/C) complete chunks
+        // section B: the last min(n_full, SW/C) complete chunks of the call go to the ring slots behind the tail (data if
+        // the chunk is a sliding one, else zeros + invalid); slots the call does not reach keep what they held
         const int n_upd = min(p.n_full, p.SW / p.C);
         const int n_fills = n_upd * p.C;
         const int src0 = (p.n_full - n_upd) * p.C;
@@ -219,18 +300,29 @@ __global__ void __launch_bounds__(kCopyThreads) evict_compact_kernel(const Compa
         for (int i = trow; i < kTokPerBlock; i += tpp) {
             const int slot = s0 + i;
             if (slot >= p.SW) break;
-            bool sw = false;
-            if (slot < n_fills) sw = roles[(src0 + slot) / p.C] == NATS_ROLE_SLIDING;
+            const int j = (slot - p.tail + p.SW) % p.SW;          // position in the write order of this call
             const size_t dst = (size_t)slot * p.rowB + tvec;
-            const size_t src = (size_t)(src0 + slot) * p.rowB + tvec;
-            st16(ck + dst, sw ? ld16_stream(k + src) : zero);
-            st16(cv + dst, sw ? ld16_stream(v + src) : zero);
-            if (tvec == 0) valid[slot] = sw ? 1 : 0;
+            if (j < n_fills) {
+                const bool sw = roles[(src0 + j) / p.C] == NATS_ROLE_SLIDING;
+                const size_t src = (size_t)(p.src_off + src0 + j) * p.rowB + tvec;
+                st16(ck + dst, sw ? ld16_stream(k + src) : zero);
+                st16(cv + dst, sw ? ld16_stream(v + src) : zero);
+                if (tvec == 0) valid[slot] = sw ? 1 : 0;
+            } else if (past) {
+                st16(ck + dst, ld16_stream(k + dst));
+                st16(cv + dst, ld16_stream(v + dst));
+                if (tvec == 0) valid[slot] = p.old_valid[(size_t)bh * p.src_stride + slot];
+            } else {
+                st16(ck + dst, zero);
+                st16(cv + dst, zero);
+                if (tvec == 0) valid[slot] = 0;
+            }
         }
         return;
     }
     blk -= p.nB;
-    // section C: destination-driven: [len, Lcap) is zero except the tokens of the unfinished chunk at [T0, T0+rem)
+    // section C: destination-driven.  [SW, base*C) = what the cache kept from before this call; [base*C, len) is written by
+    // section A; [len, Lcap) is zero except the tokens of the unfinished chunk at [T0, T0+rem)
     const int len = (int)(p.size_global[bh] + p.size_local[bh]);
     const int T0 = p.state[0];
     const int rem = p.N - p.n_full * p.C;
@@ -240,16 +332,50 @@ __global__ void __launch_bounds__(kCopyThreads) evict_compact_kernel(const Compa
         if (d >= p.Lcap) break;
         const bool in_tail = d >= T0 && d < T0 + rem;
         if (tvec == 0) valid[d] = (d < len || in_tail) ? 1 : 0;
-        if (d < len) continue;
         const size_t dst = (size_t)d * p.rowB + tvec;
+        if (d < len) {
+            if (past && d < base * p.C) {
+                st16(ck + dst, ld16_stream(k + dst));
+                st16(cv + dst, ld16_stream(v + dst));
+            }
+            continue;
+        }
         if (in_tail) {
-            const size_t src = (size_t)(p.n_full * p.C + (d - T0)) * p.rowB + tvec;
+            const size_t src = (size_t)(p.src_off + p.n_full * p.C + (d - T0)) * p.rowB + tvec;
             st16(ck + dst, ld16_stream(k + src));
             st16(cv + dst, ld16_stream(v + src));
         } else {
             st16(ck + dst, zero);
             st16(cv + dst, zero);
         }
+    }
+}
+
+// Appends the K/V of new tokens to a cache buffer at row `pos` of every (b,h) and marks them valid.
+struct AppendParams {
+    const uint8_t* k; const uint8_t* v;          // [BH, x_len, rowB]
+    uint8_t* ck; uint8_t* cv; uint8_t* valid;    // [BH, Lcap, rowB], [BH, Lcap]
+    int x_len, pos, Lcap, rowB;
+};
+
+__global__ void __launch_bounds__(kCopyThreads) cache_append_kernel(const AppendParams p) {
+    const int bh = blockIdx.y, tid = threadIdx.x;
+    const int vpt = p.rowB >> 4, tpp = kCopyThreads / vpt;
+    const int trow = tid / vpt, tvec = (tid % vpt) << 4;
+    if (trow >= tpp) return;
+    const uint8_t* k = p.k + (size_t)bh * p.x_len * p.rowB;
+    const uint8_t* v = p.v + (size_t)bh * p.x_len * p.rowB;
+    uint8_t* ck = p.ck + ((size_t)bh * p.Lcap + p.pos) * p.rowB;
+    uint8_t* cv = p.cv + ((size_t)bh * p.Lcap + p.pos) * p.rowB;
+    uint8_t* valid = p.valid + (size_t)bh * p.Lcap + p.pos;
+    const int t0 = blockIdx.x * kTokPerBlock;
+    for (int i = trow; i < kTokPerBlock; i += tpp) {
+        const int t = t0 + i;
+        if (t >= p.x_len) break;
+        const size_t o = (size_t)t * p.rowB + tvec;
+        st16(ck + o, ld16_stream(k + o));
+        st16(cv + o, ld16_stream(v + o));
+        if (tvec == 0) valid[t] = 1;
     }
 }
 
@@ -366,7 +492,41 @@ extern "C" __attribute__((visibility("default"))) int nats_b200_evict_plan(const
     NATS_CHECK_ARG(d_roles && d_rank && d_size_global && d_size_local && d_state, "null pointer");
     const int Nc = cdiv(N, C);
     evict_plan_kernel<<<B * Hkv, kScanThreads, 0, (cudaStream_t)stream>>>(
-        d_roles, Nc, N / C, C, SW, d_rank, (long long*)d_size_global, (long long*)d_size_local, d_state);
+        d_roles, Nc, N / C, C, SW, d_rank, (long long*)d_size_global, (long long*)d_size_local, d_state, nullptr);
+    NATS_CHECK_CUDA(cudaGetLastError());
+    return NATS_OK;
+}
+
+extern "C" __attribute__((visibility("default"))) int nats_b200_role_prep_past(
+    const uint8_t* d_roles_new, const uint8_t* d_valid, const int64_t* d_size_global, const int64_t* d_size_local,
+    int B, int Hkv, int x_len, int C, int SW, int valid_stride, int t0, int fill, int tail,
+    int32_t* d_lim, int32_t* d_tile_max, int32_t* d_tile_min, int64_t* d_kept_tiles, void* stream) {
+    if (int rc = check_common(B, Hkv, x_len, C, SW)) return rc;
+    NATS_CHECK_ARG(d_roles_new && d_valid && d_size_global && d_size_local && d_lim && d_tile_max && d_tile_min, "null pointer");
+    NATS_CHECK_ARG(t0 >= SW && t0 % C == 0 && fill >= 0 && fill < C, "tail offset %d must be a chunk multiple >= the window, fill %d in [0, chunk)", t0, fill);
+    NATS_CHECK_ARG(tail >= 0 && tail < SW && tail % C == 0, "ring tail %d must be a chunk multiple inside the window %d", tail, SW);
+    NATS_CHECK_ARG(valid_stride >= SW, "the flags of a head (%d) must cover the ring (%d)", valid_stride, SW);
+    NATS_CHECK_ARG((long long)t0 + fill + x_len <= 0x7fffffffLL - 2 * (long long)(SW + C), "sequence too long");
+    PastPrepParams p;
+    p.roles = d_roles_new; p.valid = d_valid;
+    p.size_global = (const long long*)d_size_global; p.size_local = (const long long*)d_size_local;
+    p.lim = d_lim; p.tmax = d_tile_max; p.tmin = d_tile_min; p.kept = (long long*)d_kept_tiles;
+    p.Ncn = cdiv(fill + x_len, C); p.Lcap = valid_stride; p.T0 = t0; p.C = C; p.SW = SW; p.tail = tail;
+    p.Nq = x_len; p.q_off = t0 + fill; p.Nkv = t0 + fill + x_len;
+    p.Nc = cdiv(p.Nkv, C); p.Ntk = cdiv(p.Nkv, kTile); p.Nt = cdiv(x_len, kTile);
+    role_prep_past_kernel<<<B * Hkv, kScanThreads, 0, (cudaStream_t)stream>>>(p);
+    NATS_CHECK_CUDA(cudaGetLastError());
+    return NATS_OK;
+}
+
+extern "C" __attribute__((visibility("default"))) int nats_b200_evict_plan_past(
+    const uint8_t* d_roles_new, int B, int Hkv, int n_tokens, int C, int SW, int32_t* d_rank, int32_t* d_base,
+    int64_t* d_size_global, int64_t* d_size_local, int32_t* d_state, void* stream) {
+    if (int rc = check_common(B, Hkv, n_tokens, C, SW)) return rc;
+    NATS_CHECK_ARG(d_roles_new && d_rank && d_base && d_size_global && d_size_local && d_state, "null pointer");
+    evict_plan_kernel<<<B * Hkv, kScanThreads, 0, (cudaStream_t)stream>>>(
+        d_roles_new, cdiv(n_tokens, C), n_tokens / C, C, SW, d_rank, (long long*)d_size_global, (long long*)d_size_local,
+        d_state, d_base);
     NATS_CHECK_CUDA(cudaGetLastError());
     return NATS_OK;
 }
@@ -390,6 +550,7 @@ extern "C" __attribute__((visibility("default"))) int nats_b200_evict_compact(co
     NATS_CHECK_ARG(Lcap >= SW + C, "cache capacity %d is smaller than ring + one chunk (%d)", Lcap, SW + C);
     CompactParams p;
     p.k = (const uint8_t*)d_k; p.v = (const uint8_t*)d_v; p.roles = d_roles; p.rank = d_rank;
+    p.old_valid = nullptr; p.base = nullptr; p.src_stride = N; p.src_off = 0; p.tail = 0;
     p.size_global = (const long long*)d_size_global; p.size_local = (const long long*)d_size_local; p.state = d_state;
     p.ck = (uint8_t*)d_cache_k; p.cv = (uint8_t*)d_cache_v; p.valid = d_valid;
     p.N = N; p.Nc = cdiv(N, C); p.n_full = N / C; p.C = C; p.SW = SW; p.Lcap = Lcap; p.rowB = D * 2;
@@ -398,6 +559,57 @@ extern "C" __attribute__((visibility("default"))) int nats_b200_evict_compact(co
     const int nC = cdiv(Lcap - SW, kTokPerBlock);
     dim3 grid(p.nA + p.nB + nC, B * Hkv);
     evict_compact_kernel<<<grid, kCopyThreads, 0, (cudaStream_t)stream>>>(p);
+    NATS_CHECK_CUDA(cudaGetLastError());
+    return NATS_OK;
+}
+
+extern "C" __attribute__((visibility("default"))) int nats_b200_evict_compact_past(
+    const void* d_old_k, const void* d_old_v, const uint8_t* d_old_valid, int old_capacity,
+    const uint8_t* d_roles_new, const int32_t* d_rank, const int32_t* d_base,
+    const int64_t* d_size_global, const int64_t* d_size_local, const int32_t* d_state,
+    int B, int Hkv, int n_tokens, int D, int C, int SW, int t0_old, int tail_old,
+    void* d_cache_k, void* d_cache_v, uint8_t* d_valid, int Lcap, void* stream) {
+    if (int rc = check_common(B, Hkv, n_tokens, C, SW)) return rc;
+    if (int rc = check_row(D)) return rc;
+    NATS_CHECK_ARG(d_old_k && d_old_v && d_old_valid && d_roles_new && d_rank && d_base && d_size_global && d_size_local &&
+                   d_state && d_cache_k && d_cache_v && d_valid, "null pointer");
+    NATS_CHECK_ARG(((uintptr_t)d_old_k | (uintptr_t)d_old_v | (uintptr_t)d_cache_k | (uintptr_t)d_cache_v) % 16 == 0,
+                   "cache pointers must be 16-byte aligned");
+    NATS_CHECK_ARG(d_old_k != d_cache_k && d_old_v != d_cache_v && d_old_valid != d_valid, "the compaction is out of place: old and new cache must differ");
+    NATS_CHECK_ARG(t0_old >= SW && t0_old % C == 0 && (long long)t0_old + n_tokens <= old_capacity,
+                   "old cache: tail offset %d (+ %d tokens) does not fit its capacity %d", t0_old, n_tokens, old_capacity);
+    NATS_CHECK_ARG(tail_old >= 0 && tail_old < SW && tail_old % C == 0, "ring tail %d must be a chunk multiple inside the window %d", tail_old, SW);
+    NATS_CHECK_ARG(Lcap >= SW + C, "cache capacity %d is smaller than ring + one chunk (%d)", Lcap, SW + C);
+    CompactParams p;
+    p.k = (const uint8_t*)d_old_k; p.v = (const uint8_t*)d_old_v; p.old_valid = d_old_valid; p.roles = d_roles_new; p.rank = d_rank;
+    p.base = d_base; p.src_stride = old_capacity; p.src_off = t0_old; p.tail = tail_old;
+    p.size_global = (const long long*)d_size_global; p.size_local = (const long long*)d_size_local; p.state = d_state;
+    p.ck = (uint8_t*)d_cache_k; p.cv = (uint8_t*)d_cache_v; p.valid = d_valid;
+    p.N = n_tokens; p.Nc = cdiv(n_tokens, C); p.n_full = n_tokens / C; p.C = C; p.SW = SW; p.Lcap = Lcap; p.rowB = D * 2;
+    p.nA = cdiv(p.n_full * C, kTokPerBlock);
+    p.nB = cdiv(SW, kTokPerBlock);
+    const int nC = cdiv(Lcap - SW, kTokPerBlock);
+    dim3 grid(p.nA + p.nB + nC, B * Hkv);
+    evict_compact_kernel<<<grid, kCopyThreads, 0, (cudaStream_t)stream>>>(p);
+    NATS_CHECK_CUDA(cudaGetLastError());
+    return NATS_OK;
+}
+
+extern "C" __attribute__((visibility("default"))) int nats_b200_cache_append(
+    const void* d_k_new, const void* d_v_new, void* d_cache_k, void* d_cache_v, uint8_t* d_valid,
+    int B, int Hkv, int x_len, int D, int Lcap, int pos, void* stream) {
+    NATS_CHECK_ARG(B > 0 && Hkv > 0 && x_len > 0 && (long long)B * Hkv <= 65535, "bad shape B=%d Hkv=%d x_len=%d", B, Hkv, x_len);
+    if (int rc = check_row(D)) return rc;
+    NATS_CHECK_ARG(d_k_new && d_v_new && d_cache_k && d_cache_v && d_valid, "null pointer");
+    NATS_CHECK_ARG(((uintptr_t)d_k_new | (uintptr_t)d_v_new | (uintptr_t)d_cache_k | (uintptr_t)d_cache_v) % 16 == 0,
+                   "K/V and cache pointers must be 16-byte aligned");
+    NATS_CHECK_ARG(pos >= 0 && (long long)pos + x_len <= Lcap, "rows [%d, %d) do not fit the cache capacity %d", pos, pos + x_len, Lcap);
+    AppendParams p;
+    p.k = (const uint8_t*)d_k_new; p.v = (const uint8_t*)d_v_new;
+    p.ck = (uint8_t*)d_cache_k; p.cv = (uint8_t*)d_cache_v; p.valid = d_valid;
+    p.x_len = x_len; p.pos = pos; p.Lcap = Lcap; p.rowB = D * 2;
+    dim3 grid(cdiv(x_len, kTokPerBlock), B * Hkv);
+    cache_append_kernel<<<grid, kCopyThreads, 0, (cudaStream_t)stream>>>(p);
     NATS_CHECK_CUDA(cudaGetLastError());
     return NATS_OK;
 }

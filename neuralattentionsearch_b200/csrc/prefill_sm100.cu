@@ -25,10 +25,10 @@ namespace nats {
 
 constexpr int kPrefillThreads = 384;
 #ifndef NATS_REGS_LOW
-#define NATS_REGS_LOW 104
+#define NATS_REGS_LOW 72
 #endif
 #ifndef NATS_REGS_HIGH
-#define NATS_REGS_HIGH 200
+#define NATS_REGS_HIGH 216
 #endif
 // setmaxnreg split: 128 * low + 256 * high must not exceed the 384 * 168 registers of the launch
 constexpr int kRegsLow = NATS_REGS_LOW, kRegsHigh = NATS_REGS_HIGH;
@@ -56,13 +56,16 @@ enum : int { kErrQ = 1, kErrKFull, kErrVFull, kErrKEmpty, kErrVEmpty, kErrSFull,
 
 struct PrefillParams {
     __nv_bfloat16* o;                 // [B,Hq,N,D]
-    const int32_t* lim;               // [B,Hkv,Nc]
-    const int32_t* tile_max;          // [B,Hkv,Nt]
+    const int32_t* lim;               // [B,Hkv,Nc]: last query POSITION that may see KV chunk c
+    const int32_t* tile_max;          // [B,Hkv,Ntk]: max / min of lim over the chunks of a 128-row KV tile
     const int32_t* tile_min;
     int32_t* status;
     int32_t* work_counter;            // next work item; zero at launch
     int total_items;                  // B * Hkv * n_groups * Nt
-    int Hq, Hkv, N, C, Nc, Nt, nrep, n_groups;   // n_groups = ceil(nrep / 2)
+    // N query rows; query row i sits at position q_off + i of the KV sequence of Nkv rows (a first call has q_off = 0 and
+    // Nkv = N; a call over an existing cache attends to the cache rows in front of its own tokens).
+    // Nc / Ntk: chunks / 128-row tiles of the KV sequence, Nt: query tiles.
+    int Hq, Hkv, N, Nkv, q_off, C, Nc, Nt, Ntk, nrep, n_groups;   // n_groups = ceil(nrep / 2)
     float scale_log2;
 };
 
@@ -337,15 +340,18 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                 const int t = p.Nt - 1 - x;                        // heavy (late) query tiles first
                 const int grp = y % p.n_groups, hkv = y / p.n_groups;
                 const int bh = z * p.Hkv + hkv;
-                const int q_lo = t * kTile, q_hi = min(q_lo + kTile, p.N) - 1;
-                const int32_t* tmax = p.tile_max + (size_t)bh * p.Nt;
-                const int32_t* tmin = p.tile_min + (size_t)bh * p.Nt;
-                for (int s0 = 0; s0 <= t; s0 += 32) {              // ordered compaction of the tiles 0..t with a visible entry
+                // positions of the first and last query row of the tile; KV tiles up to the one holding the last row
+                const int q_lo = p.q_off + t * kTile, q_hi = p.q_off + min(t * kTile + kTile, p.N) - 1;
+                const int kt_last = q_hi / kTile;
+                const int32_t* tmax = p.tile_max + (size_t)bh * p.Ntk;
+                const int32_t* tmin = p.tile_min + (size_t)bh * p.Ntk;
+                for (int s0 = 0; s0 <= kt_last; s0 += 32) {        // ordered compaction of the tiles 0..kt_last with a visible entry
                     const int kt = s0 + lane;
-                    const bool keep = kt <= t && tmax[kt] >= q_lo;
+                    const bool keep = kt <= kt_last && tmax[kt] >= q_lo;
                     const unsigned m = __ballot_sync(0xffffffffu, keep);
                     if (keep) {
-                        const bool partial = kt == t || tmin[kt] < q_hi;
+                        // element masking is needed where the causal edge or a chunk's row limit cuts through the tile
+                        const bool partial = kt * kTile + kTile - 1 > q_lo || tmin[kt] < q_hi;
                         sm.list[slot][n_kept + __popc(m & ((1u << lane) - 1u))] = (uint16_t)(kt | (partial ? 0x8000 : 0));
                     }
                     n_kept += __popc(m);
@@ -525,8 +531,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             if (h < hd.nslots) {
                 const bool pingpong = kPingPong && hd.nslots == 2;
                 const int n2 = 2 * hd.n_kept;
-                const int q_lo = hd.t * kTile;
-                const int qi = q_lo + row;                       // query token index
+                const int qpos = p.q_off + hd.t * kTile + row;   // position of this thread's query row in the KV sequence
                 const int32_t* lim = p.lim + (size_t)hd.bh * p.Nc;
                 float m_ref = -INFINITY, l_sum = 0.f;
                 for (int u = 0; u < n2; ++u, ++gu) {
@@ -538,13 +543,13 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                     uint32_t bits[2] = {0xffffffffu, 0xffffffffu};
                     if (partial) {
                         // columns this row may see: the causal prefix (and nothing past N), minus every chunk whose row limit is below it
-                        const int nvis = max(0, min(min(qi - k0 + 1, p.N - k0), kSub));
+                        const int nvis = max(0, min(min(qpos - k0 + 1, p.Nkv - k0), kSub));
 #pragma unroll
                         for (int w = 0; w < 2; ++w) bits[w] = range_mask(0, nvis, w);
                         const int c_first = k0 / p.C, c_last = min((k0 + kSub - 1) / p.C, p.Nc - 1);
 #pragma unroll 1
                         for (int cc = c_first; cc <= c_last; ++cc) {
-                            if (qi > lim[cc]) {
+                            if (qpos > lim[cc]) {
                                 const int lo = max(cc * p.C - k0, 0), hi = min((cc + 1) * p.C - k0, kSub);
 #pragma unroll
                                 for (int w = 0; w < 2; ++w) bits[w] &= ~range_mask(lo, hi, w);
@@ -636,6 +641,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                 if (ok) {
                     tc_fence_after();
                     const float inv = l_sum > 0.f ? 1.f / l_sum : 0.f;
+                    const int qi = hd.t * kTile + row;           // query row
                     __nv_bfloat16* orow = p.o + (((size_t)hd.b * p.Hq + hd.head0 + h) * p.N + qi) * D;
                     uint32_t oreg[D];
 #pragma unroll
@@ -693,11 +699,14 @@ static EncodeTiledFn get_encode_fn() {
 }
 
 // [heads, N, D] bf16 viewed as a 3-D tensor (D innermost); box = 64 x box_rows x 1 with 128-byte swizzle; rows past N read zero
-static int make_map(CUtensorMap* map, const void* base, int heads, int N, int D, int box_rows) {
+// 3-D map over [heads, rows, D] bf16; consecutive heads are head_stride_rows rows apart (>= rows: a cache buffer is
+// longer than the part of it that is valid; rows behind `rows` read as zero).
+static int make_map(CUtensorMap* map, const void* base, int heads, int N, int D, int box_rows, long long head_stride_rows = 0) {
     EncodeTiledFn fn = get_encode_fn();
     if (!fn) return fail(NATS_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+    if (head_stride_rows <= 0) head_stride_rows = N;
     cuuint64_t dims[3] = {(cuuint64_t)D, (cuuint64_t)N, (cuuint64_t)heads};
-    cuuint64_t strides[2] = {(cuuint64_t)D * 2, (cuuint64_t)N * D * 2};
+    cuuint64_t strides[2] = {(cuuint64_t)D * 2, (cuuint64_t)head_stride_rows * D * 2};
     cuuint32_t box[3] = {64, (cuuint32_t)box_rows, 1};
     cuuint32_t estr[3] = {1, 1, 1};
     CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
@@ -708,6 +717,7 @@ static int make_map(CUtensorMap* map, const void* base, int heads, int N, int D,
 }
 
 struct PrefillWs { size_t lim, tmax, tmin, counter, total; };
+// N = rows of the KV sequence
 static PrefillWs prefill_ws(int B, int Hkv, int N, int C) {
     PrefillWs w;
     const size_t Nc = cdiv(N, C), Nt = cdiv(N, kTile);
@@ -737,6 +747,29 @@ static int launch_prefill(const CUtensorMap& mq, const CUtensorMap& mk, const CU
     prefill_kernel<D><<<grid, kPrefillThreads, smem, st>>>(mq, mk, mv, p);
     NATS_CHECK_CUDA(cudaGetLastError());
     return NATS_OK;
+}
+
+// Tensor maps, parameters and launch shared by the entry points.  N query rows at positions q_off .. q_off + N - 1 of a
+// KV sequence of Nkv rows whose heads are kv_head_stride rows apart (0: contiguous).
+static int run_prefill(const void* d_q, const void* d_k, const void* d_v, void* d_o, int B, int Hq, int Hkv, int N, int Nkv,
+                       int q_off, long long kv_head_stride, int D, int C, float sm_scale, const int32_t* lim,
+                       const int32_t* tmax, const int32_t* tmin, int32_t* counter, int32_t* d_status, cudaStream_t st) {
+    CUtensorMap mq, mk, mv;
+    if (int rc = make_map(&mq, d_q, B * Hq, N, D, 128)) return rc;
+    if (int rc = make_map(&mk, d_k, B * Hkv, Nkv, D, kSub, kv_head_stride)) return rc;
+    if (int rc = make_map(&mv, d_v, B * Hkv, Nkv, D, kSub, kv_head_stride)) return rc;
+    PrefillParams p;
+    p.o = (__nv_bfloat16*)d_o; p.lim = lim; p.tile_max = tmax; p.tile_min = tmin; p.status = d_status;
+    p.Hq = Hq; p.Hkv = Hkv; p.N = N; p.Nkv = Nkv; p.q_off = q_off; p.C = C;
+    p.Nc = cdiv(Nkv, C); p.Nt = cdiv(N, kTile); p.Ntk = cdiv(Nkv, kTile);
+    p.nrep = Hq / Hkv; p.n_groups = (p.nrep + 1) / 2;
+    p.work_counter = counter;
+    const long long items = (long long)B * Hkv * p.n_groups * p.Nt;
+    NATS_CHECK_ARG(items <= 0x7fffffffLL - 65536, "too many work items (%lld)", items);
+    p.total_items = (int)items;
+    p.scale_log2 = sm_scale * 1.4426950408889634f;
+    if (D == 64) return launch_prefill<64>(mq, mk, mv, p, B, st);
+    return launch_prefill<128>(mq, mk, mv, p, B, st);
 }
 
 }  // namespace nats
@@ -769,21 +802,44 @@ extern "C" __attribute__((visibility("default"))) int nats_b200_prefill_fwd(cons
     int32_t* tmax = (int32_t*)(ws + w.tmax);
     int32_t* tmin = (int32_t*)(ws + w.tmin);
     if (int rc = nats_b200_role_prep(d_roles, B, Hkv, N, C, SW, lim, tmax, tmin, d_kept_tiles, stream)) return rc;
-    CUtensorMap mq, mk, mv;
-    if (int rc = make_map(&mq, d_q, B * Hq, N, D, 128)) return rc;
-    if (int rc = make_map(&mk, d_k, B * Hkv, N, D, kSub)) return rc;
-    if (int rc = make_map(&mv, d_v, B * Hkv, N, D, kSub)) return rc;
-    PrefillParams p;
-    p.o = (__nv_bfloat16*)d_o; p.lim = lim; p.tile_max = tmax; p.tile_min = tmin; p.status = d_status;
-    p.Hq = Hq; p.Hkv = Hkv; p.N = N; p.C = C; p.Nc = cdiv(N, C); p.Nt = cdiv(N, kTile);
-    p.nrep = Hq / Hkv; p.n_groups = (p.nrep + 1) / 2;
-    p.work_counter = (int32_t*)(ws + w.counter);
-    const long long items = (long long)B * Hkv * p.n_groups * p.Nt;
-    NATS_CHECK_ARG(items <= 0x7fffffffLL - 65536, "too many work items (%lld)", items);
-    p.total_items = (int)items;
-    p.scale_log2 = sm_scale * 1.4426950408889634f;
-    if (D == 64) return launch_prefill<64>(mq, mk, mv, p, B, (cudaStream_t)stream);
-    return launch_prefill<128>(mq, mk, mv, p, B, (cudaStream_t)stream);
+    return run_prefill(d_q, d_k, d_v, d_o, B, Hq, Hkv, N, N, 0, 0, D, C, sm_scale, lim, tmax, tmin,
+                       (int32_t*)(ws + w.counter), d_status, (cudaStream_t)stream);
+}
+
+extern "C" __attribute__((visibility("default"))) size_t nats_b200_prefill_past_workspace_bytes(int B, int Hkv, int n_kv, int C) {
+    if (B <= 0 || Hkv <= 0 || n_kv <= 0 || C <= 0) return 0;
+    return prefill_ws(B, Hkv, n_kv, C).total;
+}
+
+extern "C" __attribute__((visibility("default"))) int nats_b200_prefill_past_fwd(
+    const void* d_q, const void* d_cache_k, const void* d_cache_v, void* d_o, const uint8_t* d_roles_new,
+    const uint8_t* d_valid, int valid_stride, const int64_t* d_size_global, const int64_t* d_size_local,
+    int B, int Hq, int Hkv, int x_len, int D, int C, int SW, int cache_capacity, int t0, int fill, int tail,
+    float sm_scale, void* d_workspace, size_t workspace_bytes, int64_t* d_kept_tiles, int32_t* d_status, void* stream) {
+    NATS_CHECK_ARG(B > 0 && Hq > 0 && Hkv > 0 && x_len > 0 && Hq % Hkv == 0, "bad shape B=%d Hq=%d Hkv=%d x_len=%d", B, Hq, Hkv, x_len);
+    NATS_CHECK_ARG(C > 0 && SW > 0 && SW % C == 0, "sliding window %d must be a positive multiple of the chunk size %d", SW, C);
+    NATS_CHECK_ARG(d_q && d_cache_k && d_cache_v && d_o && d_roles_new && d_valid && d_size_global && d_size_local &&
+                   d_workspace && d_status, "null pointer");
+    NATS_CHECK_ARG(((uintptr_t)d_q | (uintptr_t)d_cache_k | (uintptr_t)d_cache_v | (uintptr_t)d_o | (uintptr_t)d_workspace) % 16 == 0,
+                   "q, the cache, o and the workspace must be 16-byte aligned");
+    NATS_CHECK_ARG(sm_scale > 0.f, "sm_scale must be positive");
+    NATS_CHECK_ARG(t0 >= SW && t0 % C == 0 && fill >= 0 && fill < C, "tail offset %d must be a multiple of the chunk size >= the window, fill %d in [0, chunk)", t0, fill);
+    NATS_CHECK_ARG(tail >= 0 && tail < SW && tail % C == 0, "ring tail %d must be a multiple of the chunk size inside the window", tail);
+    if (D != 64 && D != 128) return fail(NATS_ERR_UNSUPPORTED, "prefill supports head_dim 64 and 128, got %d", D);
+    const long long n_kv = (long long)t0 + fill + x_len;
+    NATS_CHECK_ARG(n_kv <= cache_capacity, "the cache holds %d rows, %lld are needed (the new tokens must have been appended)", cache_capacity, n_kv);
+    NATS_CHECK_ARG(n_kv <= (long long)kMaxTiles * kTile, "cache + new tokens = %lld rows exceed the prefill limit %d", n_kv, kMaxTiles * kTile);
+    const PrefillWs w = prefill_ws(B, Hkv, (int)n_kv, C);
+    if (workspace_bytes < w.total)
+        return fail(NATS_ERR_WORKSPACE, "prefill workspace: %zu bytes given, %zu needed", workspace_bytes, w.total);
+    uint8_t* ws = (uint8_t*)d_workspace;
+    int32_t* lim = (int32_t*)(ws + w.lim);
+    int32_t* tmax = (int32_t*)(ws + w.tmax);
+    int32_t* tmin = (int32_t*)(ws + w.tmin);
+    if (int rc = nats_b200_role_prep_past(d_roles_new, d_valid, d_size_global, d_size_local, B, Hkv, x_len, C, SW,
+                                          valid_stride, t0, fill, tail, lim, tmax, tmin, d_kept_tiles, stream)) return rc;
+    return run_prefill(d_q, d_cache_k, d_cache_v, d_o, B, Hq, Hkv, x_len, (int)n_kv, t0 + fill, cache_capacity, D, C, sm_scale,
+                       lim, tmax, tmin, (int32_t*)(ws + w.counter), d_status, (cudaStream_t)stream);
 }
 
 // =================================================================================================

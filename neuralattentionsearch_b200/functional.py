@@ -207,10 +207,34 @@ def nats_prefill(q, k, v, end_seqs_idx, sliding_tokens, sm_scale,
                  return_masks: bool = False, block_n: int = 32):
     """Drop-in for the reference's ``nats_prefill``: returns ``(o, mask_or_None)``.
 
-    ``block_n`` is accepted and ignored (the tile shape is fixed by the tensor-core kernel).  Attention over an
-    existing compacted cache (``global_kv_size`` given) is not built yet and raises ``NotImplementedError``."""
+    ``block_n`` is accepted and ignored (the tile shape is fixed by the tensor-core kernel).
+
+    With ``global_kv_size`` given this is a multi-token call over an existing compacted cache, as the reference's
+    HAS_PAST_INFO path (nats_flashattn_fwd.py:693-722; caller hf/llama.py:235-252): ``k``/``v`` are the cache with the new
+    tokens already appended (what ``cache.update`` returned), ``n_ctx_data`` the cache's extent before the call,
+    ``valid_sw_tokens`` the ring flags [B,Hkv,SW], ``sw_token_tails`` the ring write position, and
+    ``end_seqs_idx``/``sliding_tokens`` describe the chunks from the unfinished one on."""
     if global_kv_size is not None:
-        raise NotImplementedError('prefill continuation over an existing compacted cache is not built yet')
+        assert q.shape[1] == k.shape[1] * n_rep
+        C, SW = nats_chunk_size, local_seq_max_length
+        n_ctx = int(n_ctx_data)
+        t0 = n_ctx // C * C
+        fill = n_ctx - t0
+        assert n_tokens_in_first_chunk in (0, fill), 'n_tokens_in_first_chunk contradicts n_ctx_data'
+        roles = roles_from_end_seqs(end_seqs_idx, sliding_tokens)
+        flags = valid_sw_tokens.to(torch.uint8).contiguous()
+        o = prefill_attention_past(q, k, v, flags, roles, global_kv_size, local_kv_size, t0, fill, int(sw_token_tails), C, SW,
+                                   sm_scale)
+        mask = None
+        if return_masks:
+            x_len = q.shape[2]
+            lim = layout_row_limits(roles, flags, global_kv_size, local_kv_size, x_len, t0, fill, int(sw_token_tails), C, SW)
+            L = n_ctx + x_len
+            lim_tok = lim.repeat_interleave(C, -1)[..., :L].long()
+            qpos = torch.arange(n_ctx, L, device=q.device)
+            kpos = torch.arange(L, device=q.device)
+            mask = (kpos[None, :] <= qpos[:, None])[None, None] & (qpos[None, None, :, None] <= lim_tok[:, :, None, :])
+        return o, mask
     assert q.shape[-1] == k.shape[-1] == v.shape[-1]
     assert q.shape[-1] in {16, 32, 64, 128, 256}
     assert k.shape[2] == q.shape[2]
@@ -256,6 +280,80 @@ def evict_compact(k: torch.Tensor, v: torch.Tensor, roles: torch.Tensor, rank: t
     _lib.call('nats_b200_evict_compact', _p(k), _p(v), _p(roles), _p(rank), _p(size_global), _p(size_local), _p(state),
               B, H, N, D, chunk_size, sliding_window, _p(cache_k), _p(cache_v), _p(valid), cache_k.shape[2],
               _stream(k.device))
+
+
+def cache_append(k_new: torch.Tensor, v_new: torch.Tensor, cache_k: torch.Tensor, cache_v: torch.Tensor,
+                 valid: torch.Tensor, pos: int) -> None:
+    B, H, x_len, D = k_new.shape
+    _lib.call('nats_b200_cache_append', _p(k_new), _p(v_new), _p(cache_k), _p(cache_v), _p(valid), B, H, x_len, D,
+              cache_k.shape[2], pos, _stream(k_new.device))
+
+
+def prefill_attention_past(q: torch.Tensor, cache_k: torch.Tensor, cache_v: torch.Tensor, valid: torch.Tensor,
+                           roles_new: torch.Tensor, size_global: torch.Tensor, size_local: torch.Tensor,
+                           t0: int, fill: int, tail: int, chunk_size: int, sliding_window: int,
+                           sm_scale: float | None = None, kept_tiles: torch.Tensor | None = None) -> torch.Tensor:
+    """Attention of x_len new queries over an existing compacted cache to which their K/V have been appended at rows
+    [t0+fill, t0+fill+x_len).  q [B,Hq,x_len,D]; cache_k/v [B,Hkv,capacity,D] bf16; valid uint8 [B,Hkv,capacity];
+    roles_new uint8 [B,Hkv,ceil((fill+x_len)/C)] (chunks from the unfinished one on).  Returns o like q."""
+    dev = _need_cuda(q, cache_k, cache_v, valid, roles_new)
+    B, Hq, x_len, D = q.shape
+    Hkv = cache_k.shape[1]
+    ncn = -(-(fill + x_len) // chunk_size)
+    if roles_new.shape != (B, Hkv, ncn) or roles_new.dtype != torch.uint8:
+        raise ValueError(f'roles must be uint8 [{B},{Hkv},{ncn}], got {roles_new.dtype} {tuple(roles_new.shape)}')
+    # the cache may be a view [:, :, :n] of a longer buffer: rows contiguous, heads `capacity` rows apart
+    cap = cache_k.stride(1) // D
+    for t in (cache_k, cache_v):
+        if t.dtype != torch.bfloat16 or t.stride(3) != 1 or t.stride(2) != D or t.stride(1) != cap * D or \
+                t.stride(0) != Hkv * cap * D or t.shape[2] < t0 + fill + x_len:
+            raise ValueError('the cache must be bf16 [B,Hkv,>=t0+fill+x_len,D], dense or a [:, :, :n] view of a dense buffer')
+    if valid.dtype != torch.uint8 or valid.stride(2) != 1 or valid.stride(0) != Hkv * valid.stride(1):
+        raise ValueError('valid must be uint8 [B,Hkv,>=SW] with contiguous rows')
+    qb = _as_bf16(q)
+    o = torch.empty_like(qb)
+    lib = _lib.lib()
+    nbytes = lib.nats_b200_prefill_past_workspace_bytes(B, Hkv, t0 + fill + x_len, chunk_size)
+    ws = _workspace('prefill', dev, nbytes)
+    scale = (1.0 / math.sqrt(D)) if sm_scale is None else float(sm_scale)
+    _lib.call('nats_b200_prefill_past_fwd', _p(qb), _p(cache_k), _p(cache_v), _p(o), _p(roles_new.contiguous()), _p(valid),
+              valid.stride(1), _p(size_global), _p(size_local), B, Hq, Hkv, x_len, D, chunk_size, sliding_window, cap, t0, fill,
+              tail, scale,
+              _p(ws), ws.numel(), _p(kept_tiles), _p(status_word(dev)), _stream(dev))
+    return o if q.dtype == torch.bfloat16 else o.to(q.dtype)
+
+
+def layout_row_limits(roles_new: torch.Tensor, valid: torch.Tensor, size_global: torch.Tensor, size_local: torch.Tensor,
+                      x_len: int, t0: int, fill: int, tail: int, chunk_size: int, sliding_window: int) -> torch.Tensor:
+    """int32 [B,Hkv,ceil((t0+fill+x_len)/C)]: per chunk of the cache layout + new tokens, the last query position that may
+    see it (what the kernel masks with); a debugging aid."""
+    dev = _need_cuda(roles_new, valid)
+    B, H, _ = roles_new.shape
+    n_kv = t0 + fill + x_len
+    lim = torch.empty(B, H, -(-n_kv // chunk_size), dtype=torch.int32, device=dev)
+    nt = -(-n_kv // 128)
+    tmax = torch.empty(B, H, nt, dtype=torch.int32, device=dev)
+    tmin = torch.empty_like(tmax)
+    _lib.call('nats_b200_role_prep_past', _p(roles_new.contiguous()), _p(valid), _p(size_global), _p(size_local), B, H, x_len,
+              chunk_size, sliding_window, valid.stride(1), t0, fill, tail, _p(lim), _p(tmax), _p(tmin), None, _stream(dev))
+    return lim
+
+
+def evict_plan_past(roles_new: torch.Tensor, n_tokens: int, chunk_size: int, sliding_window: int, rank: torch.Tensor,
+                    base: torch.Tensor, size_global: torch.Tensor, size_local: torch.Tensor, state: torch.Tensor) -> None:
+    B, H, _ = roles_new.shape
+    _lib.call('nats_b200_evict_plan_past', _p(roles_new), B, H, n_tokens, chunk_size, sliding_window, _p(rank), _p(base),
+              _p(size_global), _p(size_local), _p(state), _stream(roles_new.device))
+
+
+def evict_compact_past(old_k: torch.Tensor, old_v: torch.Tensor, old_valid: torch.Tensor, roles_new: torch.Tensor,
+                       rank: torch.Tensor, base: torch.Tensor, size_global: torch.Tensor, size_local: torch.Tensor,
+                       state: torch.Tensor, n_tokens: int, chunk_size: int, sliding_window: int, t0_old: int, tail_old: int,
+                       cache_k: torch.Tensor, cache_v: torch.Tensor, valid: torch.Tensor) -> None:
+    B, H, cap_old, D = old_k.shape
+    _lib.call('nats_b200_evict_compact_past', _p(old_k), _p(old_v), _p(old_valid), cap_old, _p(roles_new), _p(rank), _p(base),
+              _p(size_global), _p(size_local), _p(state), B, H, n_tokens, D, chunk_size, sliding_window, t0_old, tail_old,
+              _p(cache_k), _p(cache_v), _p(valid), cache_k.shape[2], _stream(old_k.device))
 
 
 def decode_workspace_bytes(B: int, Hq: int, Hkv: int, D: int, max_len: int) -> int:

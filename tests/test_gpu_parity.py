@@ -164,8 +164,6 @@ def test_reference_named_entry_points():
                         local_seq_max_length=16)
     check_status(dev())
     assert_close_attn(o3, orc.prefill_attention(q, k, v, roles1, 1, 16), 'nats_attention')
-    with pytest.raises(NotImplementedError):
-        nats_prefill(qd, kd, vd, fill, sliding, 0.1, nats_chunk_size=C, global_kv_size=torch.zeros(1, 2))
 
 
 # ------------------------------------------------------------------------------------------------ eviction
