@@ -390,6 +390,36 @@ def main():
     e2e_value = flops * world / (float(t.item()) / e2e_steps * 1e-3) / 1e12
     check_status(device)
 
+    # ---- second 32k segment of the same sequence over the compacted cache of the first ----
+    continuation = None
+    if not args.no_decode:
+        q2, k2, v2, roles2 = (t.to(device) for t in make_prefill_inputs(w, w['seed'] + 1000 + rank))
+        kept2 = torch.zeros(w['B'], w['Hkv'], dtype=torch.int64, device=device)
+        times = []
+        for i in range(2 + 3):
+            _, lc2 = step(q, k, v)
+            ev4 = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+            torch.cuda.synchronize(device)
+            ev4[0].record()
+            lc2.update(k2, v2, roles2)
+            ev4[1].record()
+            lc2.prefill_attention(q2, kept_tiles=kept2)
+            ev4[2].record()
+            lc2.post_update(w['N'])
+            ev4[3].record()
+            torch.cuda.synchronize(device)
+            if i >= 2:
+                times.append([ev4[j].elapsed_time(ev4[j + 1]) for j in range(3)])
+        check_status(device)
+        tm = np.array(times).mean(0)
+        n_kept2 = int(kept2.sum().item())
+        fl2 = 4.0 * 128 * 128 * w['D'] * (w['Hq'] // w['Hkv']) * n_kept2
+        continuation = dict(metric='prefill TFLOP/s on kept tiles, second 32k segment over the compacted cache of the first',
+                            value=fl2 / (tm[1] * 1e-3) / 1e12, unit='TFLOP/s', kept_tiles=n_kept2,
+                            ms_append=float(tm[0]), ms_attention=float(tm[1]), ms_eviction=float(tm[2]),
+                            cache_rows_after=int(lc2.n_ctx_data), per_gpu=True)
+        del q2, k2, v2, lc2
+
     # ---- decode leg ----
     decode = None
     if not args.no_decode:
@@ -436,7 +466,7 @@ def main():
                     eviction=dict(ms=ms_evict, bytes=ev_bytes, gbs=ev_bytes / (ms_evict * 1e-3) / 1e9,
                                   retained_frac=(ev_tokens - w['B'] * w['Hkv'] * w['SW']) / (w['B'] * w['Hkv'] * w['N']),
                                   note='plan + one size read-back + compaction; launch-latency bound at this size'),
-                    decode=decode, cpu_baseline=cpu)
+                    decode=decode, continuation=continuation, cpu_baseline=cpu)
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()

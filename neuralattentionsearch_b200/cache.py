@@ -325,6 +325,13 @@ class NAtSCache:
             return 0
         return self.cache_model[layer_idx]._seen_tokens
 
+    # what a Hugging Face model asks of the object passed as ``past_key_values`` (the reference derives from DynamicCache)
+    is_compileable = False
+
+    def get_mask_sizes(self, query_length, layer_idx: int = 0):
+        n = query_length.shape[0] if isinstance(query_length, torch.Tensor) else int(query_length)
+        return self.get_seq_length(layer_idx) + n, 0
+
     def generate_mask(self, layer_idx: int, x_len: int):
         return self.cache_model[layer_idx].generate_mask(x_len)
 

@@ -1,0 +1,111 @@
+"""The Hugging Face caller: a random-init Llama with the NAtS attention patch in every layer, on the GPU.
+
+Per layer, the attention module's output is checked against an fp32 evaluation (module's own projections, RoPE, the
+oracle's mask for the roles the module chose).  Across calls, the identity of the path is checked at model level:
+feeding the tokens in segments and single steps gives the hidden states of one call.
+"""
+import numpy as np
+import pytest
+import torch
+
+from oracle import nats_oracle as orc
+from test_gpu_parity import dev
+
+pytestmark = pytest.mark.gpu
+
+
+def tiny_llama(layers=2, hidden=256, heads=4, kv_heads=2, head_dim=64, seed=0):
+    from transformers import LlamaConfig, LlamaForCausalLM
+    torch.manual_seed(seed)
+    cfg = LlamaConfig(hidden_size=hidden, intermediate_size=2 * hidden, num_hidden_layers=layers, num_attention_heads=heads,
+                      num_key_value_heads=kv_heads, head_dim=head_dim, vocab_size=512, max_position_embeddings=8192)
+    return LlamaForCausalLM(cfg).to(dev()).bfloat16().eval()
+
+
+def test_patched_llama_layers_match_oracle_and_segments_match_one_call():
+    from neuralattentionsearch_b200 import NAtSCache, check_status
+    from neuralattentionsearch_b200.hf import TransformerArgs, apply_rotary_pos_emb, enable_llama_nats_chunk_eval
+    C, SW, N = 16, 64, 420
+    model = tiny_llama()
+    enable_llama_nats_chunk_eval(model, TransformerArgs(n_msks=2, chunk_size=C, local_seq_max_length=SW))
+    torch.manual_seed(3)
+    for layer in model.model.layers:                          # role heads with a spread of roles
+        layer.self_attn.proj_layer.weight.data.normal_(0, 0.5)
+    ids = torch.randint(0, 512, (2, N), device=dev())
+    captured = []
+
+    def hook(mod, args, kwargs, output):
+        captured.append((kwargs['hidden_states'].detach(), kwargs['position_embeddings'], mod.token_states.detach(), output[0].detach()))
+
+    handles = [layer.self_attn.register_forward_hook(hook, with_kwargs=True) for layer in model.model.layers]
+    with torch.no_grad():
+        cache = NAtSCache(SW, C)
+        h_one = model.model(input_ids=ids, past_key_values=cache, use_cache=True).last_hidden_state
+    check_status(dev())
+    for h in handles:
+        h.remove()
+    assert len(captured) == 2
+    cfg = model.config
+    for li, (x, (cos, sin), info, out) in enumerate(captured):
+        att = model.model.layers[li].self_attn
+        roles = info.argmax(-1).cpu().numpy().astype(np.uint8)
+        assert (roles[..., 0] == 0).all() and (roles[..., -1] == 0).all()      # sink chunk and unfinished chunk
+        assert len(np.unique(roles)) == 3
+        xf = x.float()
+        q = (xf @ att.q_proj.weight.float().T).view(2, N, cfg.num_attention_heads, 64).transpose(1, 2)
+        k = (xf @ att.k_proj.weight.float().T).view(2, N, cfg.num_key_value_heads, 64).transpose(1, 2)
+        v = (xf @ att.v_proj.weight.float().T).view(2, N, cfg.num_key_value_heads, 64).transpose(1, 2)
+        q, k = apply_rotary_pos_emb(q, k, cos.float(), sin.float())
+        ref = orc.prefill_attention(q.cpu(), k.cpu(), v.cpu(), roles, C, SW)
+        ref = ref.transpose(1, 2).reshape(2, N, -1).to(dev()) @ att.o_proj.weight.float().T
+        err = (out.float() - ref).abs()
+        assert err.max().item() < 5e-2 and err.mean().item() / ref.abs().mean().item() < 2e-2, (li, err.max().item())
+        lc = cache.cache_model[li]
+        assert lc.get_seq_length() == N and lc.chunk_fill_size == N % C
+    # the same tokens in segments and single steps
+    with torch.no_grad():
+        cache2 = NAtSCache(SW, C)
+        outs, pos = [], 0
+        for n in [200, 150, 1, 1, 1, 30, 37]:
+            outs.append(model.model(input_ids=ids[:, pos:pos + n], past_key_values=cache2, use_cache=True).last_hidden_state)
+            pos += n
+    check_status(dev())
+    h_seg = torch.cat(outs, 1)
+    err = (h_seg.float() - h_one.float()).abs()
+    assert err.mean().item() / h_one.float().abs().mean().item() < 2e-2, err.mean().item()
+    for a, b in zip(cache.cache_model, cache2.cache_model):
+        assert torch.equal(a.size_global_kv, b.size_global_kv) and torch.equal(a.size_local_kv, b.size_local_kv)
+
+
+def test_full_depth_decoder_prefill_and_greedy_decode():
+    """A 32-layer decoder with the Llama-3-8B attention shape (32 query / 8 kv heads, head_dim 128) and NAtS attention in
+    every layer, hidden size cut to 1024 so that the test stays short: prefill 4096 tokens, then greedy decoding; the
+    caches of all layers hold what their sizes say and the retained fraction is far below the sequence length."""
+    from neuralattentionsearch_b200 import NAtSCache, check_status
+    from neuralattentionsearch_b200.hf import TransformerArgs, enable_llama_nats_chunk_eval
+    C, SW, N, steps, B = 128, 1024, 4096, 40, 2
+    model = tiny_llama(layers=32, hidden=1024, heads=32, kv_heads=8, head_dim=128, seed=1)
+    enable_llama_nats_chunk_eval(model, TransformerArgs(n_msks=8, chunk_size=C, local_seq_max_length=SW))
+    torch.manual_seed(5)
+    for layer in model.model.layers:
+        w = layer.self_attn.proj_layer.weight.data
+        w.normal_(0, 0.3)
+    ids = torch.randint(0, 512, (B, N), device=dev())
+    cache = NAtSCache(SW, C)
+    with torch.no_grad():
+        out = model(input_ids=ids, past_key_values=cache, use_cache=True, logits_to_keep=1)
+        tok = out.logits[:, -1].argmax(-1, keepdim=True)
+        for _ in range(steps):
+            out = model(input_ids=tok, past_key_values=cache, use_cache=True)
+            tok = out.logits[:, -1].argmax(-1, keepdim=True)
+    check_status(dev())
+    assert torch.isfinite(out.logits.float()).all()
+    assert len(cache.cache_model) == 32
+    for lc in cache.cache_model:
+        assert lc.get_seq_length() == N + steps and lc.chunk_fill_size == steps % C
+        kept = (lc.size_global_kv + lc.size_local_kv - SW).float().mean().item()
+        assert kept < 0.8 * N
+        n = lc.n_ctx_data
+        flags = lc.valid_tokens[:, :, SW:n].sum(-1)
+        want = lc.size_global_kv + lc.size_local_kv - SW + lc.chunk_fill_size
+        assert torch.equal(flags, want)

@@ -108,3 +108,31 @@ dist.destroy_process_group()
                          capture_output=True, text=True, env=env, timeout=300)
     assert res.returncode == 0, res.stderr[-2000:]
     assert 'PAIRS [12, 12]' in res.stdout
+
+
+def test_hf_patch_attaches_role_heads_and_samples_roles():
+    """The Hugging Face caller on CPU as far as it goes without kernels: module attributes, the attention-implementation
+    name that keeps the model from building a dense mask, and the role decisions incl. the pooled-x carry across calls."""
+    from transformers import LlamaConfig, LlamaForCausalLM
+    from neuralattentionsearch_b200 import NAtSCache
+    from neuralattentionsearch_b200.hf import (ATTN_IMPLEMENTATION, TransformerArgs, enable_llama_nats_chunk_eval,
+                                               sample_token_states_info)
+    torch.manual_seed(0)
+    cfg = LlamaConfig(hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+                      num_key_value_heads=2, head_dim=16, vocab_size=100)
+    model = LlamaForCausalLM(cfg).eval()
+    enable_llama_nats_chunk_eval(model, TransformerArgs(n_msks=2, chunk_size=4, local_seq_max_length=8))
+    assert model.config._attn_implementation == ATTN_IMPLEMENTATION
+    att = model.model.layers[1].self_attn
+    assert att.proj_layer.weight.shape == (2 * 3, 64) and att.chunk_size == 4 and att.local_seq_max_length == 8
+    assert 'model.layers.1.self_attn.proj_layer.weight' in model.state_dict()
+    cache = NAtSCache(8, 4)
+    x = torch.randn(2, 10, 64)
+    info = sample_token_states_info(att, x, cache, start_pos=0)
+    assert info.shape == (2, 2, 3, 3) and (info.sum(-1) == 1).all()
+    assert (info[:, :, 0, 0] == 1).all() and (info[:, :, -1, 0] == 1).all()       # sink chunk, unfinished chunk
+    pooled = x[:, 4:8].mean(1)
+    want = att.proj_layer(pooled).view(2, 2, 3).argmax(-1)
+    assert torch.equal(info[:, :, 1].argmax(-1), want)
+    with pytest.raises(TypeError):
+        att(hidden_states=x, position_embeddings=(x, x), past_key_values=None)
