@@ -232,6 +232,21 @@ int nats_b200_decode_place(const uint8_t* d_roles, void* d_cache_k, void* d_cach
                            int64_t* d_size_global, int64_t* d_size_local, int32_t* d_state,
                            int tail, int B, int Hkv, int D, int C, int SW, void* stream);
 
+/* ------------------------------------------------------------------------------------------------
+ * Caller-side helper: rotary position embedding fused with the head split, in front of the attention kernels.
+ * Replaces, in the reference's attention modules and Hugging Face patches, the chain
+ * ``proj(x).view(B,N,H,D).transpose(1,2)`` + ``apply_rotary_pos_emb`` + ``.contiguous()``
+ * (src/nats/models/transformer/hf/llama_nats_chunk.py:187-192,227,246; attention/base_attention.py:153-161).
+ *   d_q_in [B,N,Hq*D], d_k_in,d_v_in [B,N,Hkv*D] bf16, rows *_token_stride elements apart (so a fused qkv projection works);
+ *   d_cos,d_sin bf16 [B or 1, N, D] (cos_batch_stride 0 when shared), the layout of Hugging Face rotary embeddings;
+ *   d_q_out [B,Hq,N,D], d_k_out,d_v_out [B,Hkv,N,D] bf16.  rotate_half convention: pairs (i, i + D/2).
+ *   Products and sum are rounded to bf16 one by one, which reproduces the element-wise bf16 chain bit for bit.
+ */
+int nats_b200_rope_split_heads(const void* d_q_in, const void* d_k_in, const void* d_v_in, long long q_token_stride,
+                               long long k_token_stride, long long v_token_stride, const void* d_cos, const void* d_sin,
+                               long long cos_batch_stride, void* d_q_out, void* d_k_out, void* d_v_out,
+                               int B, int N, int Hq, int Hkv, int D, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -31,6 +31,8 @@ SIGNATURES = {
     'nats_b200_evict_plan_past': (_I, [_P, _I, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P]),
     'nats_b200_evict_compact_past': (_I, [_P, _P, _P, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I,
                                           _P, _P, _P, _I, _P]),
+    'nats_b200_rope_split_heads': (_I, [_P, _P, _P, _c.c_longlong, _c.c_longlong, _c.c_longlong, _P, _P, _c.c_longlong, _P, _P, _P,
+                                        _I, _I, _I, _I, _I, _P]),
     'nats_b200_decode_workspace_bytes': (_SZ, [_I, _I, _I, _I, _I]),
     'nats_b200_decode_fwd': (_I, [_P, _P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _P, _SZ, _P]),
     'nats_b200_decode_place': (_I, [_P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P]),

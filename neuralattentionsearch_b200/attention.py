@@ -110,10 +110,16 @@ class BaseNAtSChunkAttentionLayer(nn.Module):
         if self.training:
             raise NotImplementedError('this build covers inference; the training path (gumbel roles + backward) is out of scope')
         xq, xk, xv = self.wq(x), self.wk(x), self.wv(x)
+        token_states_info = self._sample_for_token_info_values_inference(x, start_pos=start_pos, cache=cache)
+        if pos_emb is not None and x.is_cuda and type(self).add_rotary_emb is BaseNAtSChunkAttentionLayer.add_rotary_emb \
+                and self.head_dim % 16 == 0:
+            # rotary embedding and head split in one pass over the projections (bit-identical to the chain below in bf16)
+            xq, xk, xv = F_.rope_split_heads(xq, xk, xv, pos_emb[0], pos_emb[1], self.n_local_heads, self.n_local_kv_heads,
+                                             self.head_dim)
+            return xq, xk, xv, {'token_states_info': token_states_info}
         xq = xq.view(bsz, seqlen, self.n_local_heads, self.head_dim).transpose(1, 2)
         xk = xk.view(bsz, seqlen, self.n_local_kv_heads, self.head_dim).transpose(1, 2)
         xv = xv.view(bsz, seqlen, self.n_local_kv_heads, self.head_dim).transpose(1, 2)
-        token_states_info = self._sample_for_token_info_values_inference(x, start_pos=start_pos, cache=cache)
         xq, xk = self.add_rotary_emb(xq, xk, pos_emb)
         return xq, xk, xv, {'token_states_info': token_states_info}
 

@@ -12,7 +12,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, 'csrc')
 LIB = os.path.join(HERE, 'libnats_b200.so')
-SOURCES = ['cache_ops.cu', 'decode.cu', 'prefill_sm100.cu']
+SOURCES = ['cache_ops.cu', 'decode.cu', 'prefill_sm100.cu', 'rope.cu']
 NVCC_FLAGS = ['-gencode', 'arch=compute_100a,code=sm_100a', '-lineinfo', '-O3', '-std=c++17',
               '-Xcompiler', '-fPIC', '-Xcompiler', '-fvisibility=hidden', '--use_fast_math']
 

@@ -263,6 +263,31 @@ def nats_attention(q, k, v, seq_info, end_seqs_idx, causal, sm_scale, n_rep: int
     return prefill_attention(q, k, v, roles, 1, local_seq_max_length, sm_scale)
 
 
+def rope_split_heads(q_in: torch.Tensor, k_in: torch.Tensor, v_in: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor,
+                     n_heads: int, n_kv_heads: int, head_dim: int):
+    """Rotary embedding + head split in one pass.  q_in [B,N,Hq*D], k_in / v_in [B,N,Hkv*D] as the projections leave them
+    (rows may be slices of a wider fused projection); cos / sin [B or 1,N,D] (Hugging Face layout).  Returns bf16
+    q [B,Hq,N,D], k, v [B,Hkv,N,D], bit-identical to ``apply_rotary_pos_emb`` on the transposed views in bf16."""
+    dev = _need_cuda(q_in, k_in, v_in, cos, sin)
+    B, N, _ = q_in.shape
+    ins = []
+    for t, h in ((q_in, n_heads), (k_in, n_kv_heads), (v_in, n_kv_heads)):
+        if t.dtype != torch.bfloat16 or t.stride(2) != 1 or t.stride(0) != N * t.stride(1) or t.shape[2] != h * head_dim:
+            t = t.to(torch.bfloat16).contiguous()
+        ins.append(t)
+    cos = cos.to(torch.bfloat16).contiguous()
+    sin = sin.to(torch.bfloat16).contiguous()
+    if cos.shape[-2:] != (N, head_dim) or cos.shape != sin.shape or cos.numel() not in (N * head_dim, B * N * head_dim):
+        raise ValueError(f'cos / sin must be [1 or {B}, {N}, {head_dim}], got {tuple(cos.shape)}')
+    q = torch.empty(B, n_heads, N, head_dim, dtype=torch.bfloat16, device=dev)
+    k = torch.empty(B, n_kv_heads, N, head_dim, dtype=torch.bfloat16, device=dev)
+    v = torch.empty_like(k)
+    _lib.call('nats_b200_rope_split_heads', _p(ins[0]), _p(ins[1]), _p(ins[2]), ins[0].stride(1), ins[1].stride(1),
+              ins[2].stride(1), _p(cos), _p(sin), 0 if cos.numel() == N * head_dim else N * head_dim, _p(q), _p(k), _p(v),
+              B, N, n_heads, n_kv_heads, head_dim, _stream(dev))
+    return q, k, v
+
+
 # ------------------------------------------------------------------------------------------------
 # thin wrappers of the cache entry points (used by cache.py)
 # ------------------------------------------------------------------------------------------------

@@ -77,16 +77,15 @@ def forward_llama_nats_chunk_one_way(self, hidden_states: torch.Tensor, position
     bsz, q_len, _ = hidden_states.shape
     cfg = self.config
     hd = self.head_dim
-    q = self.q_proj(hidden_states).view(bsz, q_len, cfg.num_attention_heads, hd).transpose(1, 2)
-    k = self.k_proj(hidden_states).view(bsz, q_len, cfg.num_key_value_heads, hd).transpose(1, 2)
-    v = self.v_proj(hidden_states).view(bsz, q_len, cfg.num_key_value_heads, hd).transpose(1, 2)
     start_pos = cache.get_seq_length(self.layer_idx)
     info = sample_token_states_info(self, hidden_states, cache, start_pos)
     self.token_states = info
     if position_embeddings is None:
         raise ValueError('position_embeddings (cos, sin) are required')
     cos, sin = position_embeddings
-    q, k = apply_rotary_pos_emb(q, k, cos, sin)
+    # projections stay [B, N, H*D]; one kernel rotates q / k and writes the [B, H, N, D] tensors the attention reads
+    q, k, v = F_.rope_split_heads(self.q_proj(hidden_states), self.k_proj(hidden_states), self.v_proj(hidden_states), cos, sin,
+                                  cfg.num_attention_heads, cfg.num_key_value_heads, hd)
     if self.post_update_is_done is not None:
         self.post_update_is_done.result()
         self.post_update_is_done = None

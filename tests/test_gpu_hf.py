@@ -109,3 +109,27 @@ def test_full_depth_decoder_prefill_and_greedy_decode():
         flags = lc.valid_tokens[:, :, SW:n].sum(-1)
         want = lc.size_global_kv + lc.size_local_kv - SW + lc.chunk_fill_size
         assert torch.equal(flags, want)
+
+
+@pytest.mark.parametrize('B,N,Hq,Hkv,D,fused_qkv,shared', [(2, 300, 4, 2, 64, False, True), (1, 1000, 32, 8, 128, True, True),
+                                                          (3, 77, 6, 2, 128, False, False), (2, 1, 8, 8, 16, False, True)])
+def test_rope_split_heads_is_bit_identical_to_the_elementwise_chain(B, N, Hq, Hkv, D, fused_qkv, shared):
+    from neuralattentionsearch_b200.functional import rope_split_heads
+    from neuralattentionsearch_b200.hf import apply_rotary_pos_emb
+    g = torch.Generator(device=dev()).manual_seed(N)
+    if fused_qkv:
+        qkv = torch.randn(B, N, (Hq + 2 * Hkv) * D, generator=g, device=dev()).bfloat16()
+        q_in, k_in, v_in = qkv[..., :Hq * D], qkv[..., Hq * D:(Hq + Hkv) * D], qkv[..., (Hq + Hkv) * D:]
+    else:
+        q_in, k_in, v_in = (torch.randn(B, N, h * D, generator=g, device=dev()).bfloat16() for h in (Hq, Hkv, Hkv))
+    pos = torch.arange(N, device=dev()).float()[None] + (0 if shared else torch.arange(B, device=dev()).float()[:, None] * 13)
+    inv = 1.0 / (10000 ** (torch.arange(0, D, 2, device=dev()).float() / D))
+    freqs = pos[..., None] * inv
+    emb = torch.cat([freqs, freqs], -1)
+    cos, sin = emb.cos().bfloat16(), emb.sin().bfloat16()
+    q, k, v = rope_split_heads(q_in, k_in, v_in, cos, sin, Hq, Hkv, D)
+    q_ref = q_in.reshape(B, N, Hq, D).transpose(1, 2)
+    k_ref = k_in.reshape(B, N, Hkv, D).transpose(1, 2)
+    q_ref, k_ref = apply_rotary_pos_emb(q_ref, k_ref, cos, sin)
+    assert torch.equal(q, q_ref.contiguous()) and torch.equal(k, k_ref.contiguous())
+    assert torch.equal(v, v_in.reshape(B, N, Hkv, D).transpose(1, 2).contiguous())
