@@ -75,6 +75,19 @@ int nats_b200_prefill_fwd(const void* d_q, const void* d_k, const void* d_v, voi
                           void* d_workspace, size_t workspace_bytes, int64_t* d_kept_tiles, int32_t* d_status,
                           void* stream);
 
+/* The forward with the two per-row statistics the reference's training forward hands to its backward
+ * (src/nats/models/transformer/triton/nats_chunk_attention.py:319-330): M = m_i + log2(l_i), the base-2 log of the row's
+ * sum of exp2(score * sm_scale * log2 e) over its visible keys, and N_VALID_BLOCKS, the number of keys the row sees
+ * (the reference sums its mask over the blocks it computes, :131-133, which is that number).
+ *   d_lse float [B,Hq,N] (out);  d_n_visible int32 [B,Hq,N] (out);  everything else as nats_b200_prefill_fwd.
+ * nats_b200_visible_counts alone: counts from the row limits nats_b200_role_prep made.
+ */
+int nats_b200_prefill_fwd_stats(const void* d_q, const void* d_k, const void* d_v, void* d_o, const uint8_t* d_roles,
+                                int B, int Hq, int Hkv, int N, int D, int C, int SW, float sm_scale,
+                                void* d_workspace, size_t workspace_bytes, int64_t* d_kept_tiles,
+                                float* d_lse, int32_t* d_n_visible, int32_t* d_status, void* stream);
+int nats_b200_visible_counts(const int32_t* d_lim, int B, int Hq, int Hkv, int N, int C, int32_t* d_n_visible, void* stream);
+
 /* Same computation as nats_b200_prefill_fwd for callers that have no way to hand over a workspace: code running
  * where device allocation is off limits -- inside a latency-critical serving loop that must not touch the allocator,
  * in a process whose memory pool is owned and fully handed out by another framework, or in a plugin host that gives

@@ -19,6 +19,8 @@ SIGNATURES = {
     'nats_b200_role_prep': (_I, [_P, _I, _I, _I, _I, _I, _P, _P, _P, _P, _P]),
     'nats_b200_prefill_workspace_bytes': (_SZ, [_I, _I, _I, _I]),
     'nats_b200_prefill_fwd': (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _P, _SZ, _P, _P, _P]),
+    'nats_b200_prefill_fwd_stats': (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _P, _SZ, _P, _P, _P, _P, _P]),
+    'nats_b200_visible_counts': (_I, [_P, _I, _I, _I, _I, _I, _P, _P]),
     'nats_b200_prefill_static_scratch_bytes': (_SZ, []),
     'nats_b200_prefill_fwd_static': (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _P, _P, _P]),
     'nats_b200_evict_plan': (_I, [_P, _I, _I, _I, _I, _I, _P, _P, _P, _P, _P]),

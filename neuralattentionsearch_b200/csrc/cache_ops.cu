@@ -157,6 +157,22 @@ __global__ void __launch_bounds__(kScanThreads) role_prep_past_kernel(const Past
     }
 }
 
+// Number of keys every query row may see (first call): sum over the chunks in front of the row.  One thread per row of a
+// kv-head; the count is written for each query head of the group.
+__global__ void __launch_bounds__(kScanThreads)
+visible_count_kernel(const int32_t* __restrict__ lim, int Hq, int Hkv, int N, int C, int Nc, int32_t* __restrict__ out) {
+    const int bh = blockIdx.y;
+    const int q = blockIdx.x * kScanThreads + threadIdx.x;
+    if (q >= N) return;
+    lim += (size_t)bh * Nc;
+    const int c_last = q / C;
+    int n = 0;
+    for (int c = 0; c <= c_last; ++c)
+        if (q <= lim[c]) n += min(q - c * C + 1, C);
+    const int nrep = Hq / Hkv, b = bh / Hkv, hkv = bh % Hkv;
+    for (int r = 0; r < nrep; ++r) out[((size_t)b * Hq + hkv * nrep + r) * N + q] = n;
+}
+
 // =================================================================================================
 // evict_plan: keep flags -> destination ranks (ballot + prefix sum), sizes, max length
 // =================================================================================================
@@ -481,6 +497,17 @@ extern "C" __attribute__((visibility("default"))) int nats_b200_role_prep(const 
     const int Nc = cdiv(N, C), Nt = cdiv(N, kTile);
     role_prep_kernel<<<B * Hkv, kScanThreads, 0, (cudaStream_t)stream>>>(
         d_roles, Nc, N, C, SW, Nt, d_lim, d_tile_max, d_tile_min, (long long*)d_kept_tiles);
+    NATS_CHECK_CUDA(cudaGetLastError());
+    return NATS_OK;
+}
+
+extern "C" __attribute__((visibility("default"))) int nats_b200_visible_counts(const int32_t* d_lim, int B, int Hq, int Hkv, int N, int C,
+                                                                    int32_t* d_n_visible, void* stream) {
+    NATS_CHECK_ARG(B > 0 && Hq > 0 && Hkv > 0 && N > 0 && C > 0 && Hq % Hkv == 0 && (long long)B * Hkv <= 65535,
+                   "bad shape B=%d Hq=%d Hkv=%d N=%d C=%d", B, Hq, Hkv, N, C);
+    NATS_CHECK_ARG(d_lim && d_n_visible, "null pointer");
+    dim3 grid(cdiv(N, kScanThreads), B * Hkv);
+    visible_count_kernel<<<grid, kScanThreads, 0, (cudaStream_t)stream>>>(d_lim, Hq, Hkv, N, C, cdiv(N, C), d_n_visible);
     NATS_CHECK_CUDA(cudaGetLastError());
     return NATS_OK;
 }

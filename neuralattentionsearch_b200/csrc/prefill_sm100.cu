@@ -56,6 +56,7 @@ enum : int { kErrQ = 1, kErrKFull, kErrVFull, kErrKEmpty, kErrVEmpty, kErrSFull,
 
 struct PrefillParams {
     __nv_bfloat16* o;                 // [B,Hq,N,D]
+    float* lse;                       // [B,Hq,N] or nullptr: log2 of the row's sum of exp2(score * scale * log2 e)
     const int32_t* lim;               // [B,Hkv,Nc]: last query POSITION that may see KV chunk c
     const int32_t* tile_max;          // [B,Hkv,Ntk]: max / min of lim over the chunks of a 128-row KV tile
     const int32_t* tile_min;
@@ -649,6 +650,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                     tc_wait_ld();
                     tc_fence_before();
                     mbar_arrive(smem_u32(&sm.bar_o_empty[h]));
+                    if (p.lse != nullptr && qi < p.N)
+                        p.lse[((size_t)hd.b * p.Hq + hd.head0 + h) * p.N + qi] = l_sum > 0.f ? m_ref + log2f(l_sum) : -INFINITY;
                     if (qi < p.N) {
 #pragma unroll
                         for (int i = 0; i < D; i += 8) {
@@ -753,13 +756,14 @@ static int launch_prefill(const CUtensorMap& mq, const CUtensorMap& mk, const CU
 // KV sequence of Nkv rows whose heads are kv_head_stride rows apart (0: contiguous).
 static int run_prefill(const void* d_q, const void* d_k, const void* d_v, void* d_o, int B, int Hq, int Hkv, int N, int Nkv,
                        int q_off, long long kv_head_stride, int D, int C, float sm_scale, const int32_t* lim,
-                       const int32_t* tmax, const int32_t* tmin, int32_t* counter, int32_t* d_status, cudaStream_t st) {
+                       const int32_t* tmax, const int32_t* tmin, int32_t* counter, int32_t* d_status, cudaStream_t st,
+                       float* d_lse = nullptr) {
     CUtensorMap mq, mk, mv;
     if (int rc = make_map(&mq, d_q, B * Hq, N, D, 128)) return rc;
     if (int rc = make_map(&mk, d_k, B * Hkv, Nkv, D, kSub, kv_head_stride)) return rc;
     if (int rc = make_map(&mv, d_v, B * Hkv, Nkv, D, kSub, kv_head_stride)) return rc;
     PrefillParams p;
-    p.o = (__nv_bfloat16*)d_o; p.lim = lim; p.tile_max = tmax; p.tile_min = tmin; p.status = d_status;
+    p.o = (__nv_bfloat16*)d_o; p.lse = d_lse; p.lim = lim; p.tile_max = tmax; p.tile_min = tmin; p.status = d_status;
     p.Hq = Hq; p.Hkv = Hkv; p.N = N; p.Nkv = Nkv; p.q_off = q_off; p.C = C;
     p.Nc = cdiv(Nkv, C); p.Nt = cdiv(N, kTile); p.Ntk = cdiv(Nkv, kTile);
     p.nrep = Hq / Hkv; p.n_groups = (p.nrep + 1) / 2;
@@ -781,10 +785,10 @@ extern "C" __attribute__((visibility("default"))) size_t nats_b200_prefill_works
     return prefill_ws(B, Hkv, N, C).total;
 }
 
-extern "C" __attribute__((visibility("default"))) int nats_b200_prefill_fwd(const void* d_q, const void* d_k, const void* d_v, void* d_o, const uint8_t* d_roles,
-                                     int B, int Hq, int Hkv, int N, int D, int C, int SW, float sm_scale,
-                                     void* d_workspace, size_t workspace_bytes, int64_t* d_kept_tiles, int32_t* d_status,
-                                     void* stream) {
+static int prefill_first_call(const void* d_q, const void* d_k, const void* d_v, void* d_o, const uint8_t* d_roles,
+                              int B, int Hq, int Hkv, int N, int D, int C, int SW, float sm_scale,
+                              void* d_workspace, size_t workspace_bytes, int64_t* d_kept_tiles, int32_t* d_status,
+                              void* stream, float* d_lse, int32_t* d_n_visible) {
     NATS_CHECK_ARG(B > 0 && Hq > 0 && Hkv > 0 && N > 0 && Hq % Hkv == 0, "bad shape B=%d Hq=%d Hkv=%d N=%d", B, Hq, Hkv, N);
     NATS_CHECK_ARG(C > 0 && SW > 0 && SW % C == 0, "sliding window %d must be a positive multiple of the chunk size %d", SW, C);
     NATS_CHECK_ARG(d_q && d_k && d_v && d_o && d_roles && d_workspace && d_status, "null pointer");
@@ -802,9 +806,29 @@ extern "C" __attribute__((visibility("default"))) int nats_b200_prefill_fwd(cons
     int32_t* tmax = (int32_t*)(ws + w.tmax);
     int32_t* tmin = (int32_t*)(ws + w.tmin);
     if (int rc = nats_b200_role_prep(d_roles, B, Hkv, N, C, SW, lim, tmax, tmin, d_kept_tiles, stream)) return rc;
+    if (d_n_visible != nullptr)
+        if (int rc = nats_b200_visible_counts(lim, B, Hq, Hkv, N, C, d_n_visible, stream)) return rc;
     return run_prefill(d_q, d_k, d_v, d_o, B, Hq, Hkv, N, N, 0, 0, D, C, sm_scale, lim, tmax, tmin,
-                       (int32_t*)(ws + w.counter), d_status, (cudaStream_t)stream);
+                       (int32_t*)(ws + w.counter), d_status, (cudaStream_t)stream, d_lse);
 }
+
+extern "C" __attribute__((visibility("default"))) int nats_b200_prefill_fwd(const void* d_q, const void* d_k, const void* d_v, void* d_o, const uint8_t* d_roles,
+                                     int B, int Hq, int Hkv, int N, int D, int C, int SW, float sm_scale,
+                                     void* d_workspace, size_t workspace_bytes, int64_t* d_kept_tiles, int32_t* d_status,
+                                     void* stream) {
+    return prefill_first_call(d_q, d_k, d_v, d_o, d_roles, B, Hq, Hkv, N, D, C, SW, sm_scale, d_workspace, workspace_bytes,
+                              d_kept_tiles, d_status, stream, nullptr, nullptr);
+}
+
+extern "C" __attribute__((visibility("default"))) int nats_b200_prefill_fwd_stats(
+    const void* d_q, const void* d_k, const void* d_v, void* d_o, const uint8_t* d_roles,
+    int B, int Hq, int Hkv, int N, int D, int C, int SW, float sm_scale, void* d_workspace, size_t workspace_bytes,
+    int64_t* d_kept_tiles, float* d_lse, int32_t* d_n_visible, int32_t* d_status, void* stream) {
+    NATS_CHECK_ARG(d_lse != nullptr && d_n_visible != nullptr, "null pointer");
+    return prefill_first_call(d_q, d_k, d_v, d_o, d_roles, B, Hq, Hkv, N, D, C, SW, sm_scale, d_workspace, workspace_bytes,
+                              d_kept_tiles, d_status, stream, d_lse, d_n_visible);
+}
+
 
 extern "C" __attribute__((visibility("default"))) size_t nats_b200_prefill_past_workspace_bytes(int B, int Hkv, int n_kv, int C) {
     if (B <= 0 || Hkv <= 0 || n_kv <= 0 || C <= 0) return 0;

@@ -255,6 +255,29 @@ def nats_chunk_attention(q, k, v, seq_info, end_seqs_idx, causal, sm_scale, nats
     return prefill_attention(q, k, v, roles, nats_chunk_size, local_seq_max_length, sm_scale)
 
 
+def nats_chunk_attention_fwd(q, k, v, seq_info, end_seqs_idx, causal, sm_scale, nats_chunk_size: int, n_rep: int = 1,
+                             local_seq_max_length: int = 4):
+    """What the forward of the reference's autograd function computes and saves for its backward
+    (triton/nats_chunk_attention.py:987-1060): ``(o, M, n_valid_blocks)`` with ``M`` fp32 [B,Hq,N] = log2 of the row's
+    sum of exp2(scaled scores) and ``n_valid_blocks`` int32 [B,Hq,N] = visible keys per row.  The backward itself is
+    not part of this package."""
+    assert causal, 'only causal attention exists on this path'
+    roles = roles_from_token_states_info(seq_info)
+    dev = _need_cuda(q, k, v, roles)
+    B, Hq, N, D = q.shape
+    Hkv = k.shape[1]
+    qb, kb, vb = _as_bf16(q), _as_bf16(k), _as_bf16(v)
+    o = torch.empty_like(qb)
+    lse = torch.empty(B, Hq, N, dtype=torch.float32, device=dev)
+    n_vis = torch.empty(B, Hq, N, dtype=torch.int32, device=dev)
+    lib = _lib.lib()
+    ws = _workspace('prefill', dev, lib.nats_b200_prefill_workspace_bytes(B, Hkv, N, nats_chunk_size))
+    _lib.call('nats_b200_prefill_fwd_stats', _p(qb), _p(kb), _p(vb), _p(o), _p(roles), B, Hq, Hkv, N, D, nats_chunk_size,
+              local_seq_max_length, float(sm_scale), _p(ws), ws.numel(), None, _p(lse), _p(n_vis), _p(status_word(dev)),
+              _stream(dev))
+    return (o if q.dtype == torch.bfloat16 else o.to(q.dtype)), lse, n_vis
+
+
 def nats_attention(q, k, v, seq_info, end_seqs_idx, causal, sm_scale, n_rep: int = 1,
                    sparse_regularized_value: float = 0., local_seq_max_length: int = 4):
     """Token-granular variant (chunk size 1) of ``nats_chunk_attention``."""

@@ -162,6 +162,27 @@ def prefill_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, roles: 
     return torch.cat(outs, dim=2)
 
 
+def prefill_stats(q: torch.Tensor, k: torch.Tensor, roles: np.ndarray, C: int, SW: int,
+                  sm_scale: float | None = None, block: int = 1024) -> tuple[torch.Tensor, np.ndarray]:
+    """The two per-row statistics the reference's training forward stores for its backward
+    (triton/nats_chunk_attention.py:131-133, 319-330): ``M = m_i + log2(l_i)`` = log2 of the sum over the visible keys of
+    exp2(q.k * sm_scale * log2 e), fp32 [B,Hq,N], and ``N_VALID_BLOCKS`` = number of visible keys per row (the mask summed
+    over the computed blocks), int32 [B,Hq,N].  The mask is the eager one, as everywhere in this file."""
+    B, Hq, N, D = q.shape
+    Hkv = k.shape[1]
+    n_rep = Hq // Hkv
+    scale = (1.0 / math.sqrt(D) if sm_scale is None else sm_scale) * 1.4426950408889634
+    lse, cnt = [], []
+    for r0 in range(0, N, block):
+        r1 = min(N, r0 + block)
+        m = torch.from_numpy(visible_mask(roles, C, SW, N, r0, r1)[..., :r1])            # [B,Hkv,rows,r1]
+        s = torch.einsum('bhqd,bhkd->bhqk', q[:, :, r0:r1].float(), k[:, :, :r1].float().repeat_interleave(n_rep, 1)) * scale
+        s = s.masked_fill(~m.repeat_interleave(n_rep, 1), float('-inf'))
+        lse.append(torch.logsumexp(s * math.log(2.0), -1) / math.log(2.0))
+        cnt.append(m.sum(-1).repeat_interleave(n_rep, 1).numpy().astype(np.int32))
+    return torch.cat(lse, 2), np.concatenate(cnt, 2)
+
+
 # --------------------------------------------------------------------------------------------
 # per-layer chunk cache state machine
 # --------------------------------------------------------------------------------------------

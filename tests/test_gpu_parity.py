@@ -166,6 +166,24 @@ def test_reference_named_entry_points():
     assert_close_attn(o3, orc.prefill_attention(q, k, v, roles1, 1, 16), 'nats_attention')
 
 
+@pytest.mark.parametrize('B,Hq,Hkv,N,D,C,SW', [(2, 4, 2, 1000, 64, 16, 64), (1, 8, 2, 2048, 128, 128, 512), (1, 2, 2, 333, 128, 1, 16)])
+def test_forward_statistics_for_the_backward(B, Hq, Hkv, N, D, C, SW):
+    """o, M (log2-sum-exp per row) and the visible-key counts of the training forward's contract."""
+    from neuralattentionsearch_b200 import check_status
+    from neuralattentionsearch_b200.functional import nats_chunk_attention_fwd, prefill_attention
+    roles = orc.make_roles(B, Hkv, -(-N // C), 0.1, 0.3, seed=N)
+    roles[..., -1] = 0                                   # training marks the first and the last chunk global
+    q, k, v = inputs(B, Hq, Hkv, N, D, seed=N + 1)
+    qd, kd, vd = (t.to(dev()).bfloat16() for t in (q, k, v))
+    o, lse, cnt = nats_chunk_attention_fwd(qd, kd, vd, orc.onehot_from_roles(roles).to(dev()), None, True, D ** -0.5, C,
+                                           n_rep=Hq // Hkv, local_seq_max_length=SW)
+    check_status(dev())
+    lse_ref, cnt_ref = orc.prefill_stats(q, k, roles, C, SW)
+    assert np.array_equal(cnt.cpu().numpy(), cnt_ref)
+    assert (lse.cpu() - lse_ref).abs().max().item() < 2e-2            # scores are bf16 products accumulated in fp32
+    assert torch.equal(o, prefill_attention(qd, kd, vd, torch.from_numpy(roles).to(dev()), C, SW))
+
+
 # ------------------------------------------------------------------------------------------------ eviction
 def run_gpu_cache(case_like, roles, k, v, dtype=torch.bfloat16):
     from neuralattentionsearch_b200.cache import NAtSChunkLayerCache

@@ -186,3 +186,17 @@ def test_decode_after_segments_matches_reference(name):
         np.testing.assert_allclose(o.numpy(), fx['dec_out'][i], rtol=1e-4, atol=2e-5, err_msg=f'step {i}')
         assert np.array_equal(np.stack([st.size_global, st.size_local]), fx['dec_sizes'][i]), f'step {i}'
     _check_state(st, fx, 'post_', full=False)
+
+
+@pytest.mark.parametrize('name', TINY)
+def test_visible_key_counts_match_the_reference_mask(name):
+    """The per-row key counts the training forward stores are the row sums of the reference's mask."""
+    case, fx, (q, k, v, _) = load(name)
+    ref = np.unpackbits(fx['prefill_mask'], axis=-1)[..., :case['N']].astype(bool)
+    lse, cnt = orc.prefill_stats(q, k, fx['roles'], case['C'], case['SW'])
+    n_rep = case['Hq'] // case['Hkv']
+    assert np.array_equal(cnt, np.repeat(ref.sum(-1), n_rep, axis=1))
+    # log-sum-exp against a direct evaluation with the reference's mask
+    s = torch.einsum('bhqd,bhkd->bhqk', q, k.repeat_interleave(n_rep, 1)) / case['D'] ** 0.5
+    s = s.masked_fill(~torch.from_numpy(np.repeat(ref, n_rep, axis=1)), float('-inf'))
+    np.testing.assert_allclose(lse.numpy(), (torch.logsumexp(s, -1) / np.log(2.0)).numpy(), rtol=1e-5, atol=1e-5)
