@@ -308,7 +308,13 @@ class NAtSChunkLayerCache:
 
 class NAtSCache:
     """Per-model container: one ``NAtSChunkLayerCache`` per layer plus the pooled hidden states the role head
-    needs across decode steps (reference: dyn_cache.py:66-195)."""
+    needs across decode steps (reference: dyn_cache.py:66-195).
+
+    ``chunk_size == 1`` is the token-granular cache (one role per token; the reference's ``NAtSLayerCache``,
+    nats_layer_cache.py:20): the same layer cache with one-token chunks.  After a prefill its sizes and kept tokens are
+    those of the reference.  Single tokens are placed as soon as they arrive, so every output follows the one-call rule
+    exactly; the reference defers placement by up to ``update_chunk_size = 16`` steps (:196-223, 300-310), during which
+    tokens stay visible past their rule, and agrees with this cache on the step after each of its batched updates."""
 
     def __init__(self, sliding_window_size: int, chunk_size: int = 1):
         self.cache_model: list[NAtSChunkLayerCache] = []
@@ -400,8 +406,6 @@ class NAtSCache:
                cache_kwargs: dict[str, Any] | None = None):
         while len(self.cache_model) <= layer_idx:
             bsz, n_kv_heads = key_states.shape[:2]
-            if self.chunk_size == 1:
-                raise NotImplementedError('the token-granular cache (chunk_size 1, deferred updates) is not built yet')
             self.cache_model.append(NAtSChunkLayerCache(bsz, n_kv_heads, self.sliding_window_size,
                                                         layer_id=len(self.cache_model), chunk_size=self.chunk_size,
                                                         device=key_states.device))

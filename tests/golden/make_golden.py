@@ -60,6 +60,14 @@ SEG_CASES = {
 }
 for _c in SEG_CASES.values():
     _c['N'] = sum(_c['segs'])
+# token-granular cache (one role per token, NAtSLayerCache): the prefill call and its eviction.  Its single-token steps
+# defer the placement of tokens by up to update_chunk_size = 16 steps, during which a token stays visible past its rule;
+# only the state right after the prefill is comparable with an implementation that places every token at once.
+TOK_CASES = {
+    'tok_tiny':    dict(B=2, Hq=4, Hkv=2, N=48,  D=16, C=1, SW=16, pg=0.10, pl=0.30, seed=41, n_decode=0),
+    'tok_long':    dict(B=2, Hq=2, Hkv=2, N=333, D=16, C=1, SW=32, pg=0.05, pl=0.30, seed=42, n_decode=0),
+    'tok_k64':     dict(B=1, Hq=4, Hkv=2, N=512, D=64, C=1, SW=64, pg=0.05, pl=0.25, seed=43, n_decode=0),
+}
 ROW_STRIDE = 5
 
 
@@ -120,6 +128,8 @@ def load_reference(root: str):
     stub('nats.models.transformer.triton.nats_chunk_attention', nats_chunk_attention=None)
     torch.cuda.get_device_capability = lambda *a, **k: (10, 0)
     torch.cuda.empty_cache = lambda *a, **k: None
+    import torch._dynamo as dynamo
+    dynamo.config.disable = True                 # the reference decorates small helpers with torch.compile; eager is the same math
     sys.path.insert(0, os.path.join(root, 'src'))
     from nats.components.cache.dyn_cache import NAtSCache
     from nats.models.transformer.attention.nats_chunk_attention import LlamaNAtSChunkAttentionLayer
@@ -261,6 +271,36 @@ def run_segmented_case(name: str, case: dict, NAtSCache, Layer) -> dict:
     return out
 
 
+def run_token_case(name: str, case: dict) -> dict:
+    """Prefill through the reference's token-granular ``NAtSLayerCache`` driven as its attention layer would
+    (update -> generate_mask -> scaled_dot_product_attention -> post_update)."""
+    from nats.components.cache.nats_layer_cache import NAtSLayerCache
+    from oracle.nats_oracle import onehot_from_roles, make_roles
+    B, Hq, Hkv, N, D, SW = (case[x] for x in ('B', 'Hq', 'Hkv', 'N', 'D', 'SW'))
+    roles = make_roles(B, Hkv, N, case['pg'], case['pl'], case['seed'], force_first_global=True)
+    q, k, v, _ = golden_inputs(case)
+    lc = NAtSLayerCache(B, Hkv, SW, device=torch.device('cpu'))
+    out = {'roles': roles, 'in_checksum': checksum(q, k, v)}
+    with torch.no_grad():
+        keys, values = lc.update(k, v, onehot_from_roles(roles))
+        mask = lc.generate_mask(N)
+        n_rep = Hq // Hkv
+        o = torch.nn.functional.scaled_dot_product_attention(q, keys.repeat_interleave(n_rep, 1), values.repeat_interleave(n_rep, 1),
+                                                             attn_mask=mask.repeat_interleave(n_rep, 1))
+        lc.post_update(N)
+    tiny = D < 64
+    out['prefill_out'] = o.numpy() if tiny else o[:, :, ::ROW_STRIDE].numpy()
+    out['prefill_mask'] = np.packbits(mask.numpy() if tiny else mask[:, :, ::ROW_STRIDE].numpy(), axis=-1)
+    out['pre_size_global'] = lc.size_global_kv.numpy().copy()
+    out['pre_size_local'] = lc.size_local_kv.numpy().copy()
+    out['pre_n_ctx_data'] = np.int64(int(lc.n_ctx_data))
+    out['pre_tail'] = np.int64(int(lc.sliding_queue_tail))
+    out['pre_valid'] = lc.valid_tokens.numpy().copy()
+    out['pre_cache_k'] = lc.cache_k.numpy().copy()
+    out['pre_cache_v'] = lc.cache_v.numpy().copy()
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument('--reference', required=True)
@@ -269,10 +309,13 @@ def main():
     sys.path.insert(0, os.path.join(HERE, '..', '..'))
     NAtSCache, Layer = load_reference(args.reference)
     only = set(filter(None, args.only.split(',')))
-    for name, case in list(CASES.items()) + list(SEG_CASES.items()):
+    for name, case in list(CASES.items()) + list(SEG_CASES.items()) + list(TOK_CASES.items()):
         if only and name not in only:
             continue
-        res = (run_segmented_case if name in SEG_CASES else run_case)(name, case, NAtSCache, Layer)
+        if name in TOK_CASES:
+            res = run_token_case(name, case)
+        else:
+            res = (run_segmented_case if name in SEG_CASES else run_case)(name, case, NAtSCache, Layer)
         path = os.path.join(HERE, name + '.npz')
         np.savez_compressed(path, **res)
         print(f'{name}: {os.path.getsize(path) / 1024:.1f} KiB')

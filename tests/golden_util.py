@@ -10,13 +10,14 @@ import make_golden  # noqa: E402  (the generator also defines how inputs are reg
 
 CASES = make_golden.CASES
 SEG_CASES = make_golden.SEG_CASES
+TOK_CASES = make_golden.TOK_CASES
 segment_roles = make_golden.segment_roles
 ROW_STRIDE = make_golden.ROW_STRIDE
 
 
 def load(name):
     """(case dict, fixture dict, (q, k, v, steps)) with the regenerated inputs checked against the stored checksums."""
-    case = CASES[name] if name in CASES else SEG_CASES[name]
+    case = CASES[name] if name in CASES else SEG_CASES[name] if name in SEG_CASES else TOK_CASES[name]
     fx = dict(np.load(os.path.join(HERE, 'golden', name + '.npz')))
     q, k, v, steps = make_golden.golden_inputs(case)
     np.testing.assert_allclose(make_golden.checksum(q, k, v), fx['in_checksum'], rtol=0, atol=1e-6,

@@ -424,6 +424,31 @@ def test_unfused_update_follows_the_reference_protocol():
     compare_cache(lc, st)
 
 
+@pytest.mark.parametrize('name', ['tok_tiny', 'tok_long', 'tok_k64'])
+def test_token_granular_prefill_matches_reference_cache(name):
+    """chunk_size 1 through the container class: sizes, kept tokens and ring of the reference's token-granular cache."""
+    from golden_util import load as load_any
+    from neuralattentionsearch_b200 import NAtSCache, check_status, prefill_attention
+    from test_oracle_golden import check_token_granular_state
+    case, fx, (q, k, v, _) = load_any(name)
+    q, k, v = bf16_round(q), bf16_round(k), bf16_round(v)
+    cache = NAtSCache(case['SW'], 1)
+    kd, vd = k.to(dev()).bfloat16(), v.to(dev()).bfloat16()
+    cache.update(kd, vd, 0, cache_kwargs={'token_states_info': orc.onehot_from_roles(fx['roles']).to(dev())})
+    if case['D'] >= 64:
+        o = prefill_attention(q.to(dev()).bfloat16(), kd, vd, torch.from_numpy(fx['roles']).to(dev()), 1, case['SW'])
+        err = (o.float().cpu()[:, :, ::ROW_STRIDE] - torch.from_numpy(fx['prefill_out'])).abs()
+        assert err.max().item() <= 4e-2
+    cache.post_update(0, case['N'])
+    check_status(dev())
+    lc = cache.cache_model[0]
+    ref_k = torch.from_numpy(fx['pre_cache_k']).bfloat16().float().numpy()
+    ref_v = torch.from_numpy(fx['pre_cache_v']).bfloat16().float().numpy()
+    fx = dict(fx, pre_cache_k=ref_k, pre_cache_v=ref_v)
+    check_token_granular_state(case, fx, lc.size_global_kv.cpu().numpy(), lc.size_local_kv.cpu().numpy(), lc.n_ctx_data,
+                               lc.valid_tokens.cpu().numpy(), lc.cache_k.float().cpu().numpy(), lc.cache_v.float().cpu().numpy())
+
+
 # ------------------------------------------------------------------------------------------------ module level
 def test_attention_layer_forward_prefill_then_decode():
     """The nn.Module with the reference's forward contract: same roles, K/V and outputs as an fp32 evaluation that
@@ -485,10 +510,12 @@ def test_prefill_full_size_spot_rows():
     assert torch.equal(o2, o[:, 4:8])
 
 
-def test_decode_equals_one_shot_prefill_on_gpu():
+@pytest.mark.parametrize('B,Hq,Hkv,D,C,SW,N0,n_steps', [(2, 8, 2, 128, 32, 128, 1024, 96),
+                                                        (2, 4, 2, 128, 1, 32, 500, 80),      # token-granular: a role per token
+                                                        (1, 8, 8, 64, 1, 16, 300, 60)])
+def test_decode_equals_one_shot_prefill_on_gpu(B, Hq, Hkv, D, C, SW, N0, n_steps):
     """prefill + eviction + decode over the compacted cache == the prefill kernel run over the whole sequence."""
     from neuralattentionsearch_b200 import check_status, prefill_attention
-    B, Hq, Hkv, D, C, SW, N0, n_steps = 2, 8, 2, 128, 32, 128, 1024, 96
     N = N0 + n_steps
     roles = orc.make_roles(B, Hkv, N // C, 0.1, 0.3, seed=8)
     q, k, v = inputs(B, Hq, Hkv, N, D, seed=9, sigma=0.5)

@@ -3,7 +3,7 @@ import numpy as np
 import pytest
 import torch
 
-from golden_util import CASES, ROW_STRIDE, SEG_CASES, load, segment_roles
+from golden_util import CASES, ROW_STRIDE, SEG_CASES, TOK_CASES, load, segment_roles
 from oracle import nats_oracle as orc
 
 TINY = [n for n, c in CASES.items() if c['D'] < 64]
@@ -200,3 +200,41 @@ def test_visible_key_counts_match_the_reference_mask(name):
     s = torch.einsum('bhqd,bhkd->bhqk', q, k.repeat_interleave(n_rep, 1)) / case['D'] ** 0.5
     s = s.masked_fill(~torch.from_numpy(np.repeat(ref, n_rep, axis=1)), float('-inf'))
     np.testing.assert_allclose(lse.numpy(), (torch.logsumexp(s, -1) / np.log(2.0)).numpy(), rtol=1e-5, atol=1e-5)
+
+
+# ---- token-granular cache (one role per token) ------------------------------------------------------------------------
+def check_token_granular_state(case, fx, size_global, size_local, n_ctx_data, valid, cache_k, cache_v, exact=True):
+    """Compares a chunk-size-1 cache after the prefill with the reference's token-granular ``NAtSLayerCache``: sizes, extent,
+    the kept tokens of every head, and the ring.  The reference's tail points at the slot written last
+    (nats_layer_cache.py:424-462), so the token N - SW + i sits in slot (tail + 1 + i) % SW there and in slot i here; it also
+    keeps the K/V of tokens that are not sliding ones with their flag cleared, so ring data is compared where valid."""
+    SW, N = case['SW'], case['N']
+    assert np.array_equal(size_global, fx['pre_size_global']) and np.array_equal(size_local, fx['pre_size_local'])
+    assert n_ctx_data == int(fx['pre_n_ctx_data'])
+    lens = size_global + size_local
+    for b in range(case['B']):
+        for h in range(case['Hkv']):
+            n = lens[b, h]
+            assert np.array_equal(valid[b, h, SW:n], fx['pre_valid'][b, h, SW:n]) and valid[b, h, SW:n].all()
+            assert np.array_equal(cache_k[b, h, SW:n], fx['pre_cache_k'][b, h, SW:n])
+            assert np.array_equal(cache_v[b, h, SW:n], fx['pre_cache_v'][b, h, SW:n])
+    shift = -(int(fx['pre_tail']) + 1)
+    ref_ring_valid = np.roll(fx['pre_valid'][:, :, :SW], shift, axis=2)
+    assert np.array_equal(valid[:, :, :SW], ref_ring_valid)
+    ref_ring_k = np.roll(fx['pre_cache_k'][:, :, :SW], shift, axis=2)
+    ref_ring_v = np.roll(fx['pre_cache_v'][:, :, :SW], shift, axis=2)
+    on = valid[:, :, :SW].astype(bool)
+    assert np.array_equal(cache_k[:, :, :SW][on], ref_ring_k[on]) and np.array_equal(cache_v[:, :, :SW][on], ref_ring_v[on])
+
+
+@pytest.mark.parametrize('name', list(TOK_CASES))
+def test_token_granular_prefill_matches_reference(name):
+    case, fx, (q, k, v, _) = load(name)
+    tiny = case['D'] < 64
+    m = orc.visible_mask(fx['roles'], 1, case['SW'], case['N'])
+    ref_mask = np.unpackbits(fx['prefill_mask'], axis=-1)[..., :case['N']].astype(bool)
+    assert np.array_equal(m if tiny else m[:, :, ::ROW_STRIDE], ref_mask)
+    st, out = _run_oracle_prefill(case, fx['roles'], q, k, v)
+    got = out.numpy() if tiny else out[:, :, ::ROW_STRIDE].numpy()
+    np.testing.assert_allclose(got, fx['prefill_out'], rtol=1e-4, atol=2e-5)
+    check_token_granular_state(case, fx, st.size_global, st.size_local, st.n_ctx_data, st.valid, st.cache_k, st.cache_v)
