@@ -305,11 +305,12 @@ def main():
     kept = torch.zeros(w['B'], w['Hkv'], dtype=torch.int64, device=device)
 
     def step(qd, kd, vd, evs=None):
+        # the reference's call order: cache.update (keeps K/V, plans the keep-set), attention, cache.post_update (compaction)
+        lc = NAtSChunkLayerCache(w['B'], w['Hkv'], w['SW'], chunk_size=w['C'], device=device)
+        lc.update(kd, vd, roles)
         o = prefill_attention(qd, kd, vd, roles, w['C'], w['SW'], kept_tiles=kept)
         if evs is not None:
             evs[1].record()
-        lc = NAtSChunkLayerCache(w['B'], w['Hkv'], w['SW'], chunk_size=w['C'], device=device)
-        lc.update(kd, vd, roles)
         lc.post_update(w['N'])
         return o, lc
 
@@ -465,7 +466,7 @@ def main():
                                     flop_per_step=flops),
                     eviction=dict(ms=ms_evict, bytes=ev_bytes, gbs=ev_bytes / (ms_evict * 1e-3) / 1e9,
                                   retained_frac=(ev_tokens - w['B'] * w['Hkv'] * w['SW']) / (w['B'] * w['Hkv'] * w['N']),
-                                  note='plan + one size read-back + compaction; launch-latency bound at this size'),
+                                  note='compaction only: the keep-set is planned in update(), ahead of the attention, and its size reaches the host while the attention runs; launch-latency bound at this size'),
                     decode=decode, continuation=continuation, cpu_baseline=cpu)
         print(json.dumps(line))
     if world > 1:

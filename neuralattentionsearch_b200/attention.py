@@ -75,7 +75,7 @@ class BaseNAtSChunkAttentionLayer(nn.Module):
     # ---- role sampling (reference: nats_chunk_attention.py:64-95, nats_attention.py:96-109) ----
     def _one_hot_global(self, like: torch.Tensor, bsz: int) -> torch.Tensor:
         oh = torch.zeros(bsz, self.n_kv_heads, 1, self.n_options, dtype=like.dtype, device=like.device)
-        oh[..., 0] = 1
+        oh[..., 0].fill_(1)
         return oh
 
     def _roles_from_pooled(self, x_pooled: torch.Tensor, start_pos: int) -> torch.Tensor:
@@ -83,7 +83,7 @@ class BaseNAtSChunkAttentionLayer(nn.Module):
         logit[..., 0] += self.global_token_enhanced_value
         index = logit.max(-1, keepdim=True)[1]
         if start_pos < self.chunk_size:
-            index[:, 0] = 0                                  # the first chunk is the attention sink
+            index[:, 0].fill_(0)                             # the first chunk is the attention sink
         samples = torch.zeros_like(logit).scatter_(-1, index, 1.0)
         return samples.transpose(1, 2).contiguous()          # [B, Hkv, Nc, 3]
 

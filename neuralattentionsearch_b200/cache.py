@@ -55,12 +55,13 @@ class NAtSChunkLayerCache:
         self._tokens_info = None
         self._roles = None
         self._state = torch.zeros(4, dtype=torch.int32, device=dev)      # [0] = common tail offset T0 (max length)
-        self._state[0] = self.sliding_window_size
+        self._state[:1].fill_(self.sliding_window_size)                 # (a kernel; indexed assignment would synchronise)
         self._t0_bound = self.sliding_window_size                       # host upper bound of T0
         self._t0_exact = self.sliding_window_size                       # exact value, None while unknown
         self._t0_synced = self.sliding_window_size                      # last exact value read back
         self._buf_k = self._buf_v = self._buf_valid = None
         self._pending = None                                            # K/V handed to update(), not yet placed
+        self._plan = None                                               # keep-set of the first call, planned in update()
         self._unposted = 0                                              # tokens seen by update() but not by post_update()
         self._dec_ws = None
 
@@ -145,6 +146,7 @@ class NAtSChunkLayerCache:
         self._roles = None if token_states_info is None else F_.roles_from_token_states_info(token_states_info)
         if self._buf_k is None and self._pending is None:
             self._pending = (key_states, value_states)
+            self._plan_ahead(x_len)
             return key_states, value_states
         kb = key_states.to(torch.bfloat16).contiguous()
         vb = value_states.to(torch.bfloat16).contiguous()
@@ -163,7 +165,7 @@ class NAtSChunkLayerCache:
         self._grow(pos + 1)
         self._buf_k[:, :, pos] = kb[:, :, 0]
         self._buf_v[:, :, pos] = vb[:, :, 0]
-        self._buf_valid[:, :, pos] = 1
+        self._buf_valid[:, :, pos].fill_(1)
         return self._buf_k[:, :, :pos + 1], self._buf_v[:, :, :pos + 1]
 
     def generate_mask(self, x_len: int) -> torch.Tensor:
@@ -269,6 +271,25 @@ class NAtSChunkLayerCache:
         self.chunk_fill_size_last = rem
         self._pending = None
 
+    def _plan_ahead(self, N: int):
+        """The keep-set of a first call depends on the roles only, so it is planned as soon as ``update`` knows them: the
+        plan kernel runs in front of the attention kernel and the size of the compacted cache travels to the host while
+        the attention runs.  ``post_update`` then finds it there instead of stalling the stream with a read-back.
+        The cache's own size tensors change in ``post_update`` only, as in the reference."""
+        C, SW = self.chunk_size, self.sliding_window_size
+        roles = self._roles
+        nc = -(-N // C)
+        if roles is None or N < C or not roles.is_cuda or roles.shape != (self.bsz, self.n_msks, nc):
+            self._plan = None
+            return
+        dev = self.device
+        rank = torch.empty(self.bsz, self.n_msks, nc, dtype=torch.int32, device=dev)
+        sg = torch.empty(self.bsz, self.n_msks, dtype=torch.long, device=dev)
+        sl = torch.empty_like(sg)
+        state = torch.zeros(4, dtype=torch.int32, device=dev)
+        F_.evict_plan(roles, N, C, SW, rank, sg, sl, state)
+        self._plan = (N, rank, sg, sl, state, F_.read_word_async(state))
+
     def _evict_after_prefill(self, x_len: int):
         C, SW = self.chunk_size, self.sliding_window_size
         k, v = self._pending
@@ -289,13 +310,19 @@ class NAtSChunkLayerCache:
             self._buf_k.zero_(); self._buf_v.zero_(); self._buf_valid.zero_()
             self._buf_k[:, :, SW:SW + N] = kb
             self._buf_v[:, :, SW:SW + N] = vb
-            self._buf_valid[:, :, SW:SW + N] = 1
+            self._buf_valid[:, :, SW:SW + N].fill_(1)
             self.chunk_fill_size_last = self.chunk_fill_size
             return
-        rank = torch.empty(B, H, nc, dtype=torch.int32, device=self.device)
-        F_.evict_plan(roles, N, C, SW, rank, self.size_global_kv, self.size_local_kv, self._state)
-        self._t0_exact = None
-        t0 = self._t0()                                           # the one host read of the prefill
+        plan, self._plan = self._plan, None
+        if plan is not None and plan[0] == N:
+            _, rank, self.size_global_kv, self.size_local_kv, self._state, wait = plan
+            t0 = wait()                                           # the 4 bytes left the device before the attention started
+            self._t0_exact = self._t0_bound = self._t0_synced = t0
+        else:
+            rank = torch.empty(B, H, nc, dtype=torch.int32, device=self.device)
+            F_.evict_plan(roles, N, C, SW, rank, self.size_global_kv, self.size_local_kv, self._state)
+            self._t0_exact = None
+            t0 = self._t0()                                       # one host read
         cap = math.ceil((t0 + rem) / C) * C + self.headroom
         self._alloc(cap, D)
         F_.evict_compact(kb, vb, roles, rank, self.size_global_kv, self.size_local_kv, self._state, C, SW,

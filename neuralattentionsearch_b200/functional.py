@@ -72,6 +72,40 @@ def _workspace(kind: str, device: torch.device, nbytes: int, zero: bool = False)
     return ws
 
 
+class _PinnedWords:
+    """A few pinned int32 words per device for small asynchronous read-backs.  Allocating pinned memory per call would
+    synchronise the device; the words are allocated once and handed out again when the copy that used them has finished."""
+    _slots: dict = {}
+
+    @classmethod
+    def read_async(cls, src: torch.Tensor):
+        """Starts copying the int32 scalar ``src[0]`` to the host on the current stream; returns ``wait() -> int``."""
+        dev = src.device
+        slots = cls._slots.setdefault(dev, [])
+        slot = None
+        for cand in slots:
+            if cand[1] is None or cand[1].query():
+                slot = cand
+                break
+        if slot is None:
+            slot = [torch.empty(1, dtype=torch.int32, pin_memory=True), None]
+            slots.append(slot)
+        slot[0].copy_(src[:1], non_blocking=True)
+        done = torch.cuda.Event()
+        done.record(torch.cuda.current_stream(dev))
+        slot[1] = done
+        host = slot[0]
+
+        def wait() -> int:
+            done.synchronize()
+            return int(host[0])
+        return wait
+
+
+def read_word_async(src: torch.Tensor):
+    return _PinnedWords.read_async(src)
+
+
 def roles_from_token_states_info(token_states_info: torch.Tensor) -> torch.Tensor:
     """uint8 role codes [B,Hkv,Nc] from the one-hot ``token_states_info`` [B,Hkv,Nc,3] (first max wins)."""
     if token_states_info.dtype == torch.uint8 and token_states_info.dim() == 3:
@@ -84,9 +118,8 @@ def roles_from_end_seqs(end_seqs_idx: torch.Tensor, sliding_tokens: torch.Tensor
     (nats_flashattn_fwd.py:96) and ``sliding_tokens`` a sliding one; everything else is local."""
     nc = end_seqs_idx.shape[-1]
     ar = torch.arange(nc, device=end_seqs_idx.device)
-    roles = torch.full(end_seqs_idx.shape, ROLE_LOCAL, dtype=torch.uint8, device=end_seqs_idx.device)
-    roles[end_seqs_idx == ar] = ROLE_GLOBAL
-    roles[sliding_tokens.to(torch.bool)] = ROLE_SLIDING
+    roles = torch.where(end_seqs_idx == ar, ROLE_GLOBAL, ROLE_LOCAL)
+    roles = torch.where(sliding_tokens.to(torch.bool), ROLE_SLIDING, roles).to(torch.uint8)
     return roles.contiguous()
 
 

@@ -55,15 +55,15 @@ def sample_token_states_info(module, hidden_states: torch.Tensor, cache: NAtSCac
     if pre + x_len < module.chunk_size:
         cache.update_nats_cached_x_in_chunk(hidden_states, module.layer_idx, module.chunk_merge_method)
         oh = torch.zeros(bsz, n_kv, 1, module.n_options, dtype=hidden_states.dtype, device=hidden_states.device)
-        oh[..., 0] = 1
+        oh[..., 0].fill_(1)
         return oh
     pooled, pad = cache.update_nats_cached_x_across_chunk(hidden_states, pre, module.layer_idx, module.chunk_merge_method)
     logit = module.proj_layer(pooled).unflatten(-1, (n_kv, module.n_options))
     index = logit.max(-1, keepdim=True)[1]
     if start_pos < module.chunk_size:
-        index[:, 0] = 0
+        index[:, 0].fill_(0)
     if pad != 0:
-        index[:, -1] = 0
+        index[:, -1].fill_(0)
     info = torch.zeros_like(logit).scatter_(-1, index, 1.0)
     return info.transpose(1, 2).contiguous()
 
