@@ -152,6 +152,41 @@ def test_segmented_equals_one_shot(B, Hq, Hkv, D, C, SW, segs, pg, pl, seed):
     assert torch.equal(aligned(lc.cache_k), lc1.cache_k[:, :, :n]) and torch.equal(aligned(lc.cache_v), lc1.cache_v[:, :, :n])
 
 
+def test_segmented_prefill_at_benchmark_size():
+    """The 32k-token benchmark shape fed as two 16k segments: outputs against one call of the kernel over all 32k tokens
+    and, on rows of several query tiles of the second segment, against the blocked fp32 oracle; same compacted cache."""
+    import bench
+    from neuralattentionsearch_b200 import check_status, prefill_attention
+    from neuralattentionsearch_b200.cache import NAtSChunkLayerCache
+    w = dict(bench.WORKLOAD)
+    B, Hq, Hkv, D, C, SW, N = w['B'], w['Hq'], w['Hkv'], w['D'], w['C'], w['SW'], w['N']
+    q, k, v, roles = bench.make_prefill_inputs(w, 123)
+    qd, kd, vd, rd = (t.to(dev()) for t in (q, k, v, roles))
+    one = prefill_attention(qd, kd, vd, rd, C, SW)
+    lc1 = NAtSChunkLayerCache(B, Hkv, SW, chunk_size=C, device=dev())
+    lc1.update(kd, vd, rd)
+    lc1.post_update(N)
+    half, hc = N // 2, N // 2 // C
+    lc = NAtSChunkLayerCache(B, Hkv, SW, chunk_size=C, device=dev())
+    keys, values = lc.update(kd[:, :, :half].contiguous(), vd[:, :, :half].contiguous(), rd[..., :hc].contiguous())
+    o_a = prefill_attention(qd[:, :, :half].contiguous(), keys, values, rd[..., :hc].contiguous(), C, SW)
+    lc.post_update(half)
+    lc.update(kd[:, :, half:].contiguous(), vd[:, :, half:].contiguous(), rd[..., hc:].contiguous())
+    o_b = lc.prefill_attention(qd[:, :, half:].contiguous())
+    lc.post_update(half)
+    check_status(dev())
+    assert_close_attn(torch.cat([o_a, o_b], 2), one, 'two segments vs one call')
+    roles_np = roles.numpy()
+    for lo in (half, half + 5000, N - 128):
+        ref = orc.prefill_attention(q.float(), k.float(), v.float(), roles_np, C, SW, rows=(lo, lo + 128))
+        assert_close_attn(o_b[:, :, lo - half:lo - half + 128], ref, f'rows {lo}..{lo + 128} vs oracle')
+    assert torch.equal(lc.size_global_kv, lc1.size_global_kv) and torch.equal(lc.size_local_kv, lc1.size_local_kv)
+    n = lc.n_ctx_data
+    assert n == lc1.n_ctx_data and lc.sliding_queue_tail == lc1.sliding_queue_tail
+    assert torch.equal(lc.cache_k[:, :, :n], lc1.cache_k[:, :, :n]) and torch.equal(lc.cache_v[:, :, :n], lc1.cache_v[:, :, :n])
+    assert torch.equal(lc.valid_tokens[:, :, :n], lc1.valid_tokens[:, :, :n])
+
+
 def test_reference_named_entry_point_with_past():
     """``nats_prefill`` with the past-information arguments of the reference (hf/llama.py:235-252)."""
     from neuralattentionsearch_b200 import nats_prefill
