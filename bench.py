@@ -134,7 +134,7 @@ class ClockSampler:
 # ---------------------------------------------------------------------------------------------- decode leg
 def build_decode_cache(d, device):
     """A compacted ragged cache as eviction leaves it: per (sequence, kv-head) a retained length drawn uniformly from
-    [len_lo, len_hi] (multiple of the chunk), ring slots valid with probability ring_p, random K/V."""
+    [len_lo, len_hi] (multiple of the chunk), each chunk of the ring valid with probability ring_p, random K/V."""
     from neuralattentionsearch_b200.cache import NAtSChunkLayerCache
     B, H, D, C, SW = d['B'], d['Hkv'], d['D'], d['C'], d['SW']
     g = torch.Generator().manual_seed(d['seed'])
@@ -149,7 +149,9 @@ def build_decode_cache(d, device):
     lc._buf_k = (torch.randn(B, H, cap, D, generator=gd, device=device) * d['sigma']).to(torch.bfloat16)
     lc._buf_v = (torch.randn(B, H, cap, D, generator=gd, device=device) * d['sigma']).to(torch.bfloat16)
     valid = torch.zeros(B, H, cap, dtype=torch.uint8, device=device)
-    valid[:, :, :SW] = (torch.rand(B, H, SW, generator=gd, device=device) < d['ring_p']).to(torch.uint8)
+    # a ring slot holds one chunk and the eviction sets its flags chunk by chunk (all tokens of a sliding chunk valid)
+    ring_chunks = (torch.rand(B, H, SW // C, generator=gd, device=device) < d['ring_p']).to(torch.uint8)
+    valid[:, :, :SW] = ring_chunks.repeat_interleave(C, -1)
     pos = torch.arange(cap, device=device)[None, None]
     valid |= ((pos >= SW) & (pos < (SW + kept).to(device)[..., None])).to(torch.uint8)
     lc._buf_valid = valid
@@ -434,7 +436,7 @@ def main():
         decode = dict(metric='decode tok/s @32k compacted KV', value=r['tokens'] * world / (dms * 1e-3), unit='tok/s',
                       ms_per_step=dms / dsteps, steps=dsteps, batch_per_gpu=DECODE['B'], gpu_launches=r['launches'],
                       config='B64 x 32q/8kv heads, head_dim 128, retained 2k-6k per (sequence, kv-head) + 1024-slot ring '
-                             '(80 % valid), chunk 128, one role per completed chunk',
+                             '(each of its 8 chunks valid with p = 0.8), chunk 128, one role per completed chunk',
                       roofline=dict(bound='hbm', achieved=gbs, peak=peaks['hbm_gbs'], unit='GB/s', frac=gbs / peaks['hbm_gbs'],
                                     traffic=traffic.get('decode_kernel'), bytes_per_step=r['kv_bytes_per_step'], of=peaks['_source']))
         if world > 1:      # NCCL only here: gather the last step's outputs of all ranks

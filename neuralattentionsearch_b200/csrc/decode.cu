@@ -100,7 +100,7 @@ __global__ void __launch_bounds__(kDecThreads) decode_kernel(const DecodeParams 
     const int r0 = seg * kSeg, r1 = min(Ltot, r0 + kSeg);
 
     extern __shared__ __align__(128) uint8_t dsm[];
-    __shared__ uint8_t s_ring_ok[kSeg];
+    __shared__ __align__(16) uint8_t s_ring_ok[kSeg];
     __shared__ int s_last;
     // after the main loop the ring memory holds the per-warp partial results
     float (*s_acc)[kMaxRep][D] = reinterpret_cast<float (*)[kMaxRep][D]>(dsm);
@@ -146,6 +146,11 @@ __global__ void __launch_bounds__(kDecThreads) decode_kernel(const DecodeParams 
         const int i0 = r0 + (it * kDecWarps + warp) * kTileTok;
         const uint32_t dst = ring + (it % kDecStages) * STAGE_BYTES;
         const int c = lane % CHUNKS, rsub = lane / CHUNKS;
+        if (i0 + kTileTok <= p.SW) {
+            // a ring tile none of whose slots is valid (a whole chunk that was not a sliding one) is not read at all
+            const uint4 f = *reinterpret_cast<const uint4*>(&s_ring_ok[i0 - r0]);
+            if ((f.x | f.y | f.z | f.w) == 0u) return;
+        }
         if (i0 + kTileTok <= len) {                      // whole tile inside ring + kept tokens: logical == physical
             const __nv_bfloat16* kp = ck + (size_t)i0 * D + c * 8;
             const __nv_bfloat16* vp = cv + (size_t)i0 * D + c * 8;
@@ -201,6 +206,7 @@ __global__ void __launch_bounds__(kDecThreads) decode_kernel(const DecodeParams 
                 ok = i < r1 && (i >= p.SW || s_ring_ok[i - r0] != 0);
             }
             vmask = __ballot_sync(FULL, ok) & 0xffffu;
+            if (vmask == 0u) continue;               // nothing visible in this tile (its copies were skipped as well)
         }
         // ---- S[heads x 16 tokens] = Q . K^T ----
         float sc[2][4];
