@@ -423,6 +423,30 @@ def main():
                             cache_rows_after=int(lc2.n_ctx_data), per_gpu=True)
         del q2, k2, v2, lc2
 
+    # ---- caller-side helper in front of the prefill: rotary embedding + head split of the projections, one pass ----
+    rope = None
+    if not args.no_decode:
+        from neuralattentionsearch_b200.functional import rope_split_heads
+        gq = torch.Generator(device=device).manual_seed(7)
+        xin = [torch.randn(w['B'], w['N'], h * w['D'], generator=gq, device=device).to(torch.bfloat16) for h in (w['Hq'], w['Hkv'], w['Hkv'])]
+        ang = torch.arange(w['N'], device=device).float()[None, :, None] / (500000.0 ** (torch.arange(0, w['D'], 2, device=device).float() / w['D']))
+        ang = torch.cat([ang, ang], -1)
+        cos_t, sin_t = ang.cos().to(torch.bfloat16), ang.sin().to(torch.bfloat16)
+        for _ in range(3):
+            rope_split_heads(*xin, cos_t, sin_t, w['Hq'], w['Hkv'], w['D'])
+        ra, rb = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize(device)
+        ra.record()
+        for _ in range(10):
+            rope_split_heads(*xin, cos_t, sin_t, w['Hq'], w['Hkv'], w['D'])
+        rb.record()
+        torch.cuda.synchronize(device)
+        rms = ra.elapsed_time(rb) / 10
+        rbytes = 2 * 2 * w['B'] * w['N'] * (w['Hq'] + 2 * w['Hkv']) * w['D']
+        rope = dict(metric='RoPE + head split of the q/k/v projections, GB/s (read + write)', value=rbytes / (rms * 1e-3) / 1e9,
+                    unit='GB/s', ms=rms, bytes=rbytes, frac_of_hbm=rbytes / (rms * 1e-3) / 1e9 / peaks['hbm_gbs'], per_gpu=True)
+        del xin, cos_t, sin_t
+
     # ---- decode leg ----
     decode = None
     if not args.no_decode:
@@ -469,7 +493,7 @@ def main():
                     eviction=dict(ms=ms_evict, bytes=ev_bytes, gbs=ev_bytes / (ms_evict * 1e-3) / 1e9,
                                   retained_frac=(ev_tokens - w['B'] * w['Hkv'] * w['SW']) / (w['B'] * w['Hkv'] * w['N']),
                                   note='compaction only: the keep-set is planned in update(), ahead of the attention, and its size reaches the host while the attention runs; launch-latency bound at this size'),
-                    decode=decode, continuation=continuation, cpu_baseline=cpu)
+                    decode=decode, continuation=continuation, rope_split_heads=rope, cpu_baseline=cpu)
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
