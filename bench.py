@@ -88,6 +88,29 @@ def make_prefill_inputs(w, seed, pin=False):
     return q, k, v, roles
 
 
+def bind_to_gpu_numa_node(index):
+    """Runs this rank on the CPUs of the NUMA node its GPU hangs off, so that the pinned host buffers of the end-to-end leg
+    are allocated in memory local to that GPU's PCIe root (ranks that share one node's memory halve each other's copy
+    bandwidth).  Returns the node, or None if the topology cannot be read."""
+    try:
+        pr = torch.cuda.get_device_properties(index)
+        bdf = '%04x:%02x:%02x.0' % (pr.pci_domain_id, pr.pci_bus_id, pr.pci_device_id)
+        node = int(open(f'/sys/bus/pci/devices/{bdf}/numa_node').read())
+        if node < 0:
+            return None
+        cpus = []
+        for part in open(f'/sys/devices/system/node/node{node}/cpulist').read().strip().split(','):
+            lo, _, hi = part.partition('-')
+            cpus += range(int(lo), int(hi or lo) + 1)
+        allowed = os.sched_getaffinity(0) & set(cpus)
+        if not allowed:
+            return None
+        os.sched_setaffinity(0, allowed)
+        return node
+    except Exception:
+        return None
+
+
 # ---------------------------------------------------------------------------------------------- clocks
 class ClockSampler:
     FIELDS = ('clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,'
@@ -293,6 +316,7 @@ def main():
         dist.init_process_group('nccl', device_id=torch.device('cuda', local_rank))
     device = torch.device('cuda', local_rank)
     torch.cuda.set_device(device)
+    numa = bind_to_gpu_numa_node(local_rank) if world > 1 else None
     peaks = load_peaks()
     traffic = load_traffic() if args.case == 'full' else {}
 
@@ -481,7 +505,8 @@ def main():
         line = dict(metric=METRIC, value=value, unit='TFLOP/s', n_gpus=world, steps=args.steps, warmup=args.warmup,
                     ms_per_step=ms_step, higher_is_better=True, scaling='weak', vs_baseline=None, dtype='bf16',
                     data='synthetic', config=config, clocks=clocks,
-                    e2e=dict(value=e2e_value, unit='TFLOP/s', h2d_bytes_per_step=h2d, d2h_bytes_per_step=d2h),
+                    e2e=dict(value=e2e_value, unit='TFLOP/s', h2d_bytes_per_step=h2d, d2h_bytes_per_step=d2h,
+                             **({'numa_node_of_rank0': numa} if numa is not None else {})),
                     gpu_launches=4 * args.steps,          # timed region: role_prep, prefill, evict_plan, evict_compact per step
                     roofline=dict(bound='tensor', achieved=tf, peak=peak, unit='TFLOP/s', frac=tf / peak, traffic=traffic.get('prefill_kernel'),
                                   kernel='prefill_kernel<128>', ms_per_launch=ms_kernel, ms_in_step=ms_prefill,
