@@ -275,13 +275,18 @@ def main():
     ap.add_argument('--impl', default='b200', choices=['b200', 'reference'])
     ap.add_argument('--no-cpu', action='store_true', help='skip the CPU baseline leg')
     ap.add_argument('--no-decode', action='store_true', help='skip the decode leg')
-    ap.add_argument('--case', default='full', choices=['full', 'small'],
+    ap.add_argument('--case', default='full', choices=['full', 'small', 'long'],
                     help="'small' = a quarter of the heads / of the decode batch: the profiling case (inputs still exceed L2); "
-                         "its line is marked and is not a benchmark value")
+                         "'long' = the 131072-token stress configuration (batch 2, window 4096, ~2 % global / 8 % local), "
+                         "prefill + eviction only; neither line is the benchmark value")
     args = ap.parse_args()
     if args.case == 'small':
         WORKLOAD.update(Hq=8, Hkv=2)
         DECODE.update(B=16)
+    if args.case == 'long':
+        WORKLOAD.update(name='prefill131k_evict', B=2, N=131072, SW=4096, p_global=0.02, p_local=0.08)
+        args.no_decode = True
+        args.no_cpu = True
 
     rank = int(os.environ.get('RANK', 0))
     world = int(os.environ.get('WORLD_SIZE', 1))
@@ -293,6 +298,10 @@ def main():
     if args.case == 'small':
         config = dict(config, workload='PROFILING CASE (not a benchmark value): 8q/2kv heads of the 32k prefill, decode batch 16',
                       l2='inputs larger than L2 (q+k+v+o = 168 MB per step)')
+    if args.case == 'long':
+        config = dict(config, workload='LONG-CONTEXT STRESS CASE (not the benchmark value): prefill 131072 + eviction, B2 x 32q/8kv heads, '
+                                       'head_dim 128, window 4096, chunk 128, roles 2/8/90 % global/local/sliding; two sequences per GPU',
+                      l2='inputs larger than L2 (q+k+v+o = 5.4 GB per step)')
 
     if args.impl == 'reference':
         if rank != 0:
@@ -502,7 +511,7 @@ def main():
     if rank == 0:
         tf = flops / (ms_kernel * 1e-3) / 1e12
         peak = peaks['bf16_tflops_sustained'] if ms_kernel * max(args.steps, 10) > 1000 else peaks['bf16_tflops']
-        line = dict(metric=METRIC, value=value, unit='TFLOP/s', n_gpus=world, steps=args.steps, warmup=args.warmup,
+        line = dict(metric=METRIC if args.case != 'long' else 'prefill TFLOP/s on kept tiles @131k', value=value, unit='TFLOP/s', n_gpus=world, steps=args.steps, warmup=args.warmup,
                     ms_per_step=ms_step, higher_is_better=True, scaling='weak', vs_baseline=None, dtype='bf16',
                     data='synthetic', config=config, clocks=clocks,
                     e2e=dict(value=e2e_value, unit='TFLOP/s', h2d_bytes_per_step=h2d, d2h_bytes_per_step=d2h,
