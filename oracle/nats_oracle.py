@@ -17,11 +17,19 @@ computes for one attention layer (paths are relative to the reference project ro
                                        src/nats/components/cache/cache_update.py:25-76
 * size / validity bookkeeping          src/nats/components/cache/nats_chunk_layer_cache.py:262-385,634-656
 * decode mask and decode attention     src/nats/components/cache/nats_chunk_layer_cache.py:622-632
+* multi-token call over a cache        src/nats/components/cache/nats_chunk_layer_cache.py:239-256,444-511,658-713 (mask),
+                                       :331-385 (eviction); one deviation, marked where it is made: the unfinished chunk
+                                       is always moved (:840 leaves it behind in one corner case)
+* training-forward statistics          src/nats/models/transformer/triton/nats_chunk_attention.py:131-133,319-330
+                                       (the log-sum-exp has no reference output to pin against: Triton only)
+* token-granular cache after a prefill src/nats/components/cache/nats_layer_cache.py (the chunk cache with one-token chunks
+                                       reproduces its sizes and kept tokens; its deferred single-token updates are not restated)
 
 Parity pin: the reference ships no golden vectors or known-answer tests for this path, so the
 oracle is pinned against outputs of the reference's own code, imported and executed on CPU by
 ``tests/golden/make_golden.py``; the resulting fixtures are committed under ``tests/golden/`` and
-checked by ``tests/test_oracle_golden.py``.
+checked by ``tests/test_oracle_golden.py`` (first calls + decode steps, segmented calls ``seg_*``,
+token-granular prefills ``tok_*``).
 
 Role codes: 0 = global, 1 = local, 2 = sliding window (column order of ``token_states_info``,
 nats_chunk_layer_cache.py:188-190).
