@@ -71,3 +71,42 @@ def test_product_refuses_cpu_tensors():
     roles = torch.zeros(1, 2, 4, dtype=torch.uint8)
     with pytest.raises(_lib.NatsB200Error):
         prefill_attention(q, q, q, roles, 16, 64)
+
+
+def test_argument_errors_of_the_multi_token_and_helper_entry_points(lib):
+    one, two = ctypes.c_void_p(256), ctypes.c_void_p(512)
+    err = lambda: lib.nats_b200_last_error()
+    # append: rows must fit the capacity
+    assert lib.nats_b200_cache_append(one, one, two, two, two, 1, 2, 100, 128, 1000, 950, None) == 1 and b'fit' in err()
+    assert lib.nats_b200_cache_append(one, one, two, two, None, 1, 2, 100, 128, 2000, 950, None) == 1 and b'null' in err()
+    # role metadata over a cache: tail offset a chunk multiple behind the window, fill inside a chunk, ring tail aligned
+    args = dict(B=1, H=2, x=100, C=16, SW=64, stride=4096)
+    call = lambda t0, fill, tail: lib.nats_b200_role_prep_past(one, one, one, one, args['B'], args['H'], args['x'], args['C'], args['SW'],
+                                                                 args['stride'], t0, fill, tail, one, one, one, None, None)
+    assert call(70, 0, 0) == 1 and b'tail offset' in err()
+    assert call(32, 0, 0) == 1
+    assert call(128, 16, 0) == 1
+    assert call(128, 3, 8) == 1 and b'ring tail' in err()
+    # attention over a cache: the new tokens must have been appended (capacity), head_dim as for a first call
+    rc = lib.nats_b200_prefill_past_fwd(one, one, one, one, one, one, 4096, one, one, 1, 4, 2, 100, 128, 16, 64, 200, 128, 3, 0, 0.1,
+                                        one, 1 << 20, None, one, None)
+    assert rc == 1 and b'appended' in err()
+    rc = lib.nats_b200_prefill_past_fwd(one, one, one, one, one, one, 4096, one, one, 1, 4, 2, 100, 32, 16, 64, 4096, 128, 3, 0, 0.1,
+                                        one, 1 << 20, None, one, None)
+    assert rc == 2 and b'head_dim' in err()
+    assert lib.nats_b200_prefill_past_workspace_bytes(1, 2, 4096, 16) % 256 == 0
+    # compaction over a cache is out of place
+    rc = lib.nats_b200_evict_compact_past(one, one, one, 4096, one, one, one, one, one, one, 1, 2, 100, 128, 16, 64, 128, 0,
+                                          one, one, one, 4096, None)
+    assert rc == 1 and b'out of place' in err()
+    rc = lib.nats_b200_evict_compact_past(one, one, one, 200, one, one, one, one, one, one, 1, 2, 100, 128, 16, 64, 128, 0,
+                                          two, two, two, 4096, None)
+    assert rc == 1 and b'capacity' in err()
+    # statistics entry point needs both outputs
+    rc = lib.nats_b200_prefill_fwd_stats(one, one, one, one, one, 1, 4, 2, 128, 128, 16, 64, 0.1, one, 1 << 20, None, None, one, one, None)
+    assert rc == 1 and b'null' in err()
+    # rotary embedding + head split: strides must cover a row of heads and keep 16-byte alignment
+    rope = lambda sq, D=128: lib.nats_b200_rope_split_heads(one, one, one, sq, 256, 256, one, one, 0, two, two, two, 1, 10, 4, 2, D, None)
+    assert rope(100) == 1 and b'stride' in err()
+    assert rope(516) == 1
+    assert rope(512, D=24) == 1 and b'head_dim' in err()
