@@ -633,3 +633,63 @@ def test_host_pipeline_equals_device_prefill():
         ref = prefill_attention(q.to(dev()), k.to(dev()), v.to(dev()), roles.to(dev()), C, SW)
         assert torch.equal(out, ref.cpu())
         assert torch.equal(pipe.k.cpu(), k) and torch.equal(pipe.roles.cpu(), roles)
+
+
+def test_batch128_prefill_16k_then_decode_configuration():
+    """The attention shape of the 32-layer decoder configuration at its full batch: 128 sequences x 16384 tokens, 32 query /
+    8 kv heads, head_dim 128, chunk 128, window 1024, roles set for ~10 % retention.  One layer: kept-tile counts and
+    eviction sizes of all 1024 (sequence, kv-head) pairs against the closed forms, rows of several query tiles against the
+    blocked fp32 oracle, and four decode steps at batch 128 against the prefill kernel run over the longer sequence."""
+    from neuralattentionsearch_b200 import check_status, prefill_attention
+    from neuralattentionsearch_b200.cache import NAtSChunkLayerCache
+    B, Hq, Hkv, N, D, C, SW, steps = 128, 32, 8, 16384, 128, 128, 1024, 4
+    roles = orc.make_roles(B, Hkv, N // C + 1, 0.03, 0.07, seed=55)
+    g = torch.Generator(device=dev()).manual_seed(55)
+
+    def rnd(h, n):
+        out = torch.empty(B, h, n, D, dtype=torch.bfloat16, device=dev())
+        for b0 in range(0, B, 16):                        # generated in slices: no fp32 copy of the whole tensor at once
+            out[b0:b0 + 16] = (torch.randn(16, h, n, D, generator=g, device=dev()) * 0.5).bfloat16()
+        return out
+
+    q, k, v = rnd(Hq, N + steps), rnd(Hkv, N + steps), rnd(Hkv, N + steps)
+    r0 = np.ascontiguousarray(roles[..., :N // C])
+    rd = torch.from_numpy(r0).to(dev())
+    kept = torch.zeros(B, Hkv, dtype=torch.int64, device=dev())
+    qn, kn, vn = q[:, :, :N].contiguous(), k[:, :, :N].contiguous(), v[:, :, :N].contiguous()
+    lc = NAtSChunkLayerCache(B, Hkv, SW, chunk_size=C, device=dev())
+    lc.update(kn, vn, rd)
+    o = prefill_attention(qn, kn, vn, rd, C, SW, kept_tiles=kept)
+    lc.post_update(N)
+    check_status(dev())
+    assert np.array_equal(kept.cpu().numpy(), orc.kept_tiles(r0, C, SW, N))
+    for (b, h, lo) in ((0, 0, 128), (77, 5, 8192), (127, 7, N - 128)):
+        sl = slice(h * 4, h * 4 + 4)
+        ref = orc.prefill_attention(qn[b:b + 1, sl, :lo + 128].float().cpu(), kn[b:b + 1, h:h + 1, :lo + 128].float().cpu(),
+                                    vn[b:b + 1, h:h + 1, :lo + 128].float().cpu(), r0[b:b + 1, h:h + 1, :(lo + 128) // C], C, SW,
+                                    rows=(lo, lo + 128), block=128)
+        assert_close_attn(o[b:b + 1, sl, lo:lo + 128], ref, f'rows {lo} of ({b},{h})')
+    del o, qn
+    n_g = (r0 == 0).sum(-1)
+    last_g = np.where(r0 == 0, np.arange(N // C), -1).max(-1)
+    n_l = ((r0 == 1) & (np.arange(N // C)[None, None] > last_g[..., None])).sum(-1)
+    assert np.array_equal(lc.size_global_kv.cpu().numpy(), SW + C * n_g)
+    assert np.array_equal(lc.size_local_kv.cpu().numpy(), C * n_l)
+    retained = float((C * (n_g + n_l)).mean()) / N
+    assert 0.05 < retained < 0.2, retained
+    # decode at batch 128; the first two sequences are checked against one call of the prefill kernel over N + steps tokens
+    outs = []
+    placeholder = torch.zeros(B, Hkv, 1, dtype=torch.uint8, device=dev())
+    for i in range(steps):
+        t = N + i
+        lc.update(k[:, :, t:t + 1].contiguous(), v[:, :, t:t + 1].contiguous(), placeholder, fused=True)
+        outs.append(lc.decode_attention(q[:, :, t:t + 1].contiguous()))
+        lc.post_update(1)
+    r2 = np.ascontiguousarray(roles[:2])
+    r2[..., -1] = 0
+    full = prefill_attention(q[:2].contiguous(), k[:2].contiguous(), v[:2].contiguous(), torch.from_numpy(r2).to(dev()), C, SW)
+    check_status(dev())
+    for i in range(steps):
+        err = (outs[i][:2].float() - full[:, :, N + i:N + i + 1].float()).abs().max().item()
+        assert err <= 2e-2, (i, err)
+    assert torch.isfinite(torch.cat(outs, 2).float()).all()
