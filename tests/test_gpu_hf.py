@@ -133,3 +133,46 @@ def test_rope_split_heads_is_bit_identical_to_the_elementwise_chain(B, N, Hq, Hk
     q_ref, k_ref = apply_rotary_pos_emb(q_ref, k_ref, cos, sin)
     assert torch.equal(q, q_ref.contiguous()) and torch.equal(k, k_ref.contiguous())
     assert torch.equal(v, v_in.reshape(B, N, Hkv, D).transpose(1, 2).contiguous())
+
+
+def test_llama3_8b_shaped_decoder_end_to_end():
+    """The decoder configuration at its real width: random-init 32 layers, hidden 4096, FFN 14336, 32 query / 8 kv heads,
+    vocabulary 128256, bf16, NAtS attention in every layer; prefill of 16384 random token ids for two sequences, then greedy
+    decoding.  Checks what can be checked without a second implementation of the whole model: finite logits, the
+    protocol state of every layer's cache, flags that agree with the sizes, and a retained fraction far below 1."""
+    from transformers import LlamaConfig, LlamaForCausalLM
+    from neuralattentionsearch_b200 import NAtSCache, check_status
+    from neuralattentionsearch_b200.hf import TransformerArgs, enable_llama_nats_chunk_eval
+    C, SW, N, steps, B = 128, 1024, 16384, 8, 2
+    cfg = LlamaConfig(hidden_size=4096, intermediate_size=14336, num_hidden_layers=32, num_attention_heads=32,
+                      num_key_value_heads=8, head_dim=128, vocab_size=128256, max_position_embeddings=32768,
+                      rope_theta=500000.0)
+    torch.manual_seed(2)
+    prev = torch.get_default_dtype()
+    torch.set_default_dtype(torch.bfloat16)
+    try:
+        with torch.device(dev()):
+            model = LlamaForCausalLM(cfg).eval()
+    finally:
+        torch.set_default_dtype(prev)
+    enable_llama_nats_chunk_eval(model, TransformerArgs(n_msks=8, chunk_size=C, local_seq_max_length=SW))
+    for layer in model.model.layers:
+        layer.self_attn.proj_layer.weight.data.normal_(0, 0.05)
+    ids = torch.randint(0, cfg.vocab_size, (B, N), device=dev())
+    cache = NAtSCache(SW, C)
+    with torch.no_grad():
+        out = model(input_ids=ids, past_key_values=cache, use_cache=True, logits_to_keep=1)
+        tok = out.logits[:, -1].argmax(-1, keepdim=True)
+        for _ in range(steps):
+            out = model(input_ids=tok, past_key_values=cache, use_cache=True)
+            tok = out.logits[:, -1].argmax(-1, keepdim=True)
+    check_status(dev())
+    assert out.logits.shape == (B, 1, cfg.vocab_size) and torch.isfinite(out.logits.float()).all()
+    assert len(cache.cache_model) == 32
+    fractions = []
+    for lc in cache.cache_model:
+        assert lc.get_seq_length() == N + steps and lc.chunk_fill_size == steps
+        want = lc.size_global_kv + lc.size_local_kv - SW + lc.chunk_fill_size
+        assert torch.equal(lc.valid_tokens[:, :, SW:lc.n_ctx_data].sum(-1), want)
+        fractions.append((lc.size_global_kv + lc.size_local_kv - SW).float().mean().item() / N)
+    assert max(fractions) < 0.9 and min(fractions) >= 0.0
