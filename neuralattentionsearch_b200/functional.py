@@ -74,36 +74,55 @@ def _workspace(kind: str, device: torch.device, nbytes: int, zero: bool = False)
 
 class _PinnedWords:
     """A few pinned int32 words per device for small asynchronous read-backs.  Allocating pinned memory per call would
-    synchronise the device; the words are allocated once and handed out again when the copy that used them has finished."""
-    _slots: dict = {}
+    synchronise the device, so the words are allocated once and handed out again when their reader is done with them."""
+    _free: dict = {}
+    _lock = __import__('threading').Lock()
 
     @classmethod
-    def read_async(cls, src: torch.Tensor):
-        """Starts copying the int32 scalar ``src[0]`` to the host on the current stream; returns ``wait() -> int``."""
-        dev = src.device
-        slots = cls._slots.setdefault(dev, [])
-        slot = None
-        for cand in slots:
-            if cand[1] is None or cand[1].query():
-                slot = cand
-                break
-        if slot is None:
-            slot = [torch.empty(1, dtype=torch.int32, pin_memory=True), None]
-            slots.append(slot)
-        slot[0].copy_(src[:1], non_blocking=True)
-        done = torch.cuda.Event()
-        done.record(torch.cuda.current_stream(dev))
-        slot[1] = done
-        host = slot[0]
+    def take(cls, dev: torch.device) -> torch.Tensor:
+        with cls._lock:
+            free = cls._free.setdefault(dev, [])
+            return free.pop() if free else torch.empty(1, dtype=torch.int32, pin_memory=True)
 
-        def wait() -> int:
-            done.synchronize()
-            return int(host[0])
-        return wait
+    @classmethod
+    def give_back(cls, dev: torch.device, word: torch.Tensor) -> None:
+        with cls._lock:
+            cls._free.setdefault(dev, []).append(word)
 
 
-def read_word_async(src: torch.Tensor):
-    return _PinnedWords.read_async(src)
+class _AsyncWord:
+    """An int32 scalar on its way from the device to the host.  Calling the object waits for the copy and returns the
+    value; the pinned word goes back to the pool when the value has been read or the object is dropped."""
+
+    def __init__(self, src: torch.Tensor):
+        self.dev = src.device
+        self.word = _PinnedWords.take(self.dev)
+        self.word.copy_(src[:1], non_blocking=True)
+        self.done = torch.cuda.Event()
+        self.done.record(torch.cuda.current_stream(self.dev))
+
+    def __call__(self) -> int:
+        self.done.synchronize()
+        value = int(self.word[0])
+        self._release()
+        return value
+
+    def _release(self):
+        if self.word is not None:
+            self.done.synchronize()          # the copy must not land in a word that somebody else already holds
+            _PinnedWords.give_back(self.dev, self.word)
+            self.word = None
+
+    def __del__(self):
+        try:
+            self._release()
+        except Exception:
+            pass
+
+
+def read_word_async(src: torch.Tensor) -> _AsyncWord:
+    """Starts copying the int32 scalar ``src[0]`` to the host on the current stream; call the result to get the value."""
+    return _AsyncWord(src)
 
 
 def roles_from_token_states_info(token_states_info: torch.Tensor) -> torch.Tensor:

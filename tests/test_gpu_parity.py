@@ -693,3 +693,26 @@ def test_batch128_prefill_16k_then_decode_configuration():
         err = (outs[i][:2].float() - full[:, :, N + i:N + i + 1].float()).abs().max().item()
         assert err <= 2e-2, (i, err)
     assert torch.isfinite(torch.cat(outs, 2).float()).all()
+
+
+def test_interleaved_caches_keep_their_own_planned_sizes():
+    """Several caches between update() and post_update() at the same time (layers whose post_update runs on a worker thread,
+    or simply a different call order): every cache gets the compacted size that was planned for it."""
+    cases = [dict(B=1, Hkv=2, N=512, D=64, C=16, SW=64), dict(B=2, Hkv=2, N=1000, D=64, C=16, SW=64),
+             dict(B=1, Hkv=4, N=300, D=64, C=32, SW=64)]
+    from neuralattentionsearch_b200.cache import NAtSChunkLayerCache
+    live = []
+    for i, c in enumerate(cases):
+        roles = orc.make_roles(c['B'], c['Hkv'], -(-c['N'] // c['C']), 0.1 + 0.1 * i, 0.3, seed=60 + i)
+        if c['N'] % c['C']:
+            roles[..., -1] = 0
+        _, k, v = inputs(c['B'], c['Hkv'], c['Hkv'], c['N'], c['D'], seed=70 + i)
+        lc = NAtSChunkLayerCache(c['B'], c['Hkv'], c['SW'], chunk_size=c['C'], device=dev(), headroom=64)
+        lc.update(k.to(dev()).bfloat16(), v.to(dev()).bfloat16(), orc.onehot_from_roles(roles).to(dev()))
+        st = orc.ChunkCacheOracle(c['B'], c['Hkv'], c['SW'], c['C'])
+        st.update(k.numpy(), v.numpy(), roles)
+        st.post_update(c['N'])
+        live.append((lc, st, c))
+    for lc, st, c in reversed(live):
+        lc.post_update(c['N'])
+        compare_cache(lc, st)
