@@ -157,6 +157,7 @@ class NAtSChunkLayerCache:
             self._grow(pos + x_len)
             F_.cache_append(kb, vb, self._buf_k, self._buf_v, self._buf_valid, pos)
             self._pending = None
+            self._plan_ahead_past()
             return self._buf_k[:, :, :pos + x_len], self._buf_v[:, :, :pos + x_len]
         self._pending = (kb, vb)
         if fused:
@@ -257,11 +258,17 @@ class NAtSChunkLayerCache:
         if roles is None or roles.shape != (B, H, -(-n_tokens // C)):
             raise ValueError(f'token_states_info must describe {-(-n_tokens // C)} chunks')
         t0_old = self._t0()
-        rank = torch.empty(B, H, roles.shape[-1], dtype=torch.int32, device=self.device)
-        base = torch.empty(B, H, dtype=torch.int32, device=self.device)
-        F_.evict_plan_past(roles, n_tokens, C, SW, rank, base, self.size_global_kv, self.size_local_kv, self._state)
-        self._t0_exact = None
-        t0 = self._t0()                                           # the one host read of the call
+        plan, self._plan = self._plan, None
+        if plan is not None and plan[0] == ('past', n_tokens):
+            _, rank, base, self.size_global_kv, self.size_local_kv, self._state, wait = plan
+            t0 = wait()                                           # planned in update(), read back while the attention ran
+            self._t0_exact = self._t0_bound = self._t0_synced = t0
+        else:
+            rank = torch.empty(B, H, roles.shape[-1], dtype=torch.int32, device=self.device)
+            base = torch.empty(B, H, dtype=torch.int32, device=self.device)
+            F_.evict_plan_past(roles, n_tokens, C, SW, rank, base, self.size_global_kv, self.size_local_kv, self._state)
+            self._t0_exact = None
+            t0 = self._t0()                                       # one host read
         old = (self._buf_k, self._buf_v, self._buf_valid)
         self._alloc(math.ceil((t0 + rem) / C) * C + self.headroom, D)
         F_.evict_compact_past(*old, roles, rank, base, self.size_global_kv, self.size_local_kv, self._state, n_tokens, C, SW,
@@ -270,6 +277,24 @@ class NAtSChunkLayerCache:
         self.chunk_fill_size = rem
         self.chunk_fill_size_last = rem
         self._pending = None
+
+    def _plan_ahead_past(self):
+        """The same for a multi-token call over an existing cache: the plan works on copies of the size tensors, because
+        the attention of this call still reads the sizes as they are."""
+        C, SW = self.chunk_size, self.sliding_window_size
+        n_tokens = self.chunk_fill_size
+        roles = self._roles
+        self._plan = None
+        if roles is None or n_tokens < C or roles.shape != (self.bsz, self.n_msks, -(-n_tokens // C)):
+            return
+        self._t0()                                                # the exact tail offset before the plan replaces the state word
+        dev = self.device
+        rank = torch.empty(self.bsz, self.n_msks, roles.shape[-1], dtype=torch.int32, device=dev)
+        base = torch.empty(self.bsz, self.n_msks, dtype=torch.int32, device=dev)
+        sg, sl = self.size_global_kv.clone(), self.size_local_kv.clone()
+        state = torch.zeros(4, dtype=torch.int32, device=dev)
+        F_.evict_plan_past(roles, n_tokens, C, SW, rank, base, sg, sl, state)
+        self._plan = (('past', n_tokens), rank, base, sg, sl, state, F_.read_word_async(state))
 
     def _plan_ahead(self, N: int):
         """The keep-set of a first call depends on the roles only, so it is planned as soon as ``update`` knows them: the
