@@ -260,6 +260,26 @@ int nats_b200_rope_split_heads(const void* d_q_in, const void* d_k_in, const voi
                                long long cos_batch_stride, void* d_q_out, void* d_k_out, void* d_v_out,
                                int B, int N, int Hq, int Hkv, int D, void* stream);
 
+/* ------------------------------------------------------------------------------------------------
+ * The decode step with static launch parameters, for callers that record the step once (a CUDA graph) and replay it.
+ * nats_b200_decode_fwd / nats_b200_decode_place take the number of tokens in the unfinished chunk and the ring position by
+ * value, so a recorded launch would freeze them; here they live in the state words: d_state is int32[8] with
+ * [4] = tokens in the unfinished chunk, [5] = ring write position ([0..3] as before).  One step is
+ *     nats_b200_decode_step_fwd(...)      append + attention (reads [4])
+ *     nats_b200_decode_step_place(...)    placement if this token completed a chunk (d_roles: its role per (b,kv-head),
+ *                                         ignored otherwise), then [4], [5] advance
+ * max_len_bound must bound d_state[0] for every replay (the cache capacity minus a chunk does); Lcap must hold
+ * max_len_bound + C rows; the workspace is sized for max_len_bound + C.
+ */
+int nats_b200_decode_step_fwd(const void* d_q, const void* d_k_new, const void* d_v_new, void* d_o,
+                              void* d_cache_k, void* d_cache_v, uint8_t* d_valid, int Lcap,
+                              const int64_t* d_size_global, const int64_t* d_size_local, const int32_t* d_state,
+                              int max_len_bound, int B, int Hq, int Hkv, int D, int C, int SW, float sm_scale,
+                              void* d_workspace, size_t workspace_bytes, void* stream);
+int nats_b200_decode_step_place(const uint8_t* d_roles, void* d_cache_k, void* d_cache_v, uint8_t* d_valid, int Lcap,
+                                int64_t* d_size_global, int64_t* d_size_local, int32_t* d_state,
+                                int B, int Hkv, int D, int C, int SW, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -37,6 +37,8 @@ SIGNATURES = {
                                         _I, _I, _I, _I, _I, _P]),
     'nats_b200_decode_workspace_bytes': (_SZ, [_I, _I, _I, _I, _I]),
     'nats_b200_decode_fwd': (_I, [_P, _P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _P, _SZ, _P]),
+    'nats_b200_decode_step_fwd': (_I, [_P, _P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _P, _SZ, _P]),
+    'nats_b200_decode_step_place': (_I, [_P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _P]),
     'nats_b200_decode_place': (_I, [_P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P]),
 }
 

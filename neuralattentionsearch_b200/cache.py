@@ -54,7 +54,7 @@ class NAtSChunkLayerCache:
         self._seen_tokens = 0
         self._tokens_info = None
         self._roles = None
-        self._state = torch.zeros(4, dtype=torch.int32, device=dev)      # [0] = common tail offset T0 (max length)
+        self._state = torch.zeros(8, dtype=torch.int32, device=dev)      # [0] = common tail offset T0 (max length)
         self._state[:1].fill_(self.sliding_window_size)                 # (a kernel; indexed assignment would synchronise)
         self._t0_bound = self.sliding_window_size                       # host upper bound of T0
         self._t0_exact = self.sliding_window_size                       # exact value, None while unknown
@@ -217,6 +217,57 @@ class NAtSChunkLayerCache:
                       self._state, fill, self._t0_bound, self.chunk_size, self.sliding_window_size, scale, self._dec_ws)
         return o if xq.dtype == torch.bfloat16 else o.to(xq.dtype)
 
+    # ------------------------------------------------------------------ decode steps with static launch parameters
+    def prepare_static_decode(self, n_steps: int, n_heads: int, head_dim: int) -> None:
+        """Gets the cache ready for ``n_steps`` calls of ``decode_step_static`` that neither allocate nor read anything
+        back, so that one such step can be recorded in a CUDA graph and replayed: buffers and workspace get room for the
+        steps, and the counters the kernels need move into the device state words."""
+        C = self.chunk_size
+        t0 = self._t0()
+        chunks = (self.chunk_fill_size + n_steps) // C + 1
+        self._grow(t0 + chunks * C + C + 1)
+        self._static_bound = self._buf_k.shape[2] - C
+        need = F_.decode_workspace_bytes(self.bsz, n_heads, self.n_msks, head_dim, self._static_bound + C)
+        if self._dec_ws is None or self._dec_ws.numel() < need:
+            self._dec_ws = torch.zeros(need, dtype=torch.uint8, device=self.device)
+        counters = torch.tensor([self.chunk_fill_size, self.sliding_queue_tail], dtype=torch.int32).to(self.device)
+        self._state[4:6].copy_(counters)
+        self._static_steps_left = n_steps
+
+    def decode_step_static(self, xq: torch.Tensor, k_new: torch.Tensor, v_new: torch.Tensor, roles: torch.Tensor,
+                           out: torch.Tensor, sm_scale: float | None = None, recording: bool = False) -> torch.Tensor:
+        """One decode step -- append, attention, placement if the token completes a chunk -- as launches whose parameters
+        do not change from step to step.  All tensors bf16 and contiguous: xq / out [B,Hq,1,D], k_new / v_new [B,Hkv,1,D];
+        roles uint8 [B,Hkv] = role of the chunk this token completes (read on the device only if it does).  The host
+        counters advance by one step.  While a graph is being recorded pass ``recording=True`` (the launches are captured, not
+        run, so the host counters stay); after replaying the recorded step n times call ``note_static_steps(n)``."""
+        D = xq.shape[-1]
+        scale = (1.0 / math.sqrt(D)) if sm_scale is None else sm_scale
+        F_.decode_step_fwd(xq, k_new, v_new, out, self._buf_k, self._buf_v, self._buf_valid, self.size_global_kv,
+                           self.size_local_kv, self._state, self._static_bound, self.chunk_size, self.sliding_window_size,
+                           scale, self._dec_ws)
+        F_.decode_step_place(roles, self._buf_k, self._buf_v, self._buf_valid, self.size_global_kv, self.size_local_kv,
+                             self._state, self.chunk_size, self.sliding_window_size)
+        if not recording:
+            self.note_static_steps(1)
+        return out
+
+    def note_static_steps(self, n: int) -> None:
+        """Advances the host's view of the cache by ``n`` decode steps that ran on the device (recorded and replayed)."""
+        if n > self._static_steps_left:
+            raise RuntimeError('more static decode steps than prepare_static_decode() made room for')
+        self._static_steps_left -= n
+        C, SW = self.chunk_size, self.sliding_window_size
+        done, fill = divmod(self.chunk_fill_size + n, C)
+        self.chunk_fill_size = self.chunk_fill_size_last = fill
+        self.sliding_queue_tail = (self.sliding_queue_tail + done * C) % SW
+        self._seen_tokens += n
+        self._unposted = 0
+        self._pending = None
+        if done:
+            self._t0_bound += done * C
+            self._t0_exact = None
+
     def post_update(self, x_len: int):
         self._seen_tokens += x_len
         self._unposted = 0
@@ -292,7 +343,7 @@ class NAtSChunkLayerCache:
         rank = torch.empty(self.bsz, self.n_msks, roles.shape[-1], dtype=torch.int32, device=dev)
         base = torch.empty(self.bsz, self.n_msks, dtype=torch.int32, device=dev)
         sg, sl = self.size_global_kv.clone(), self.size_local_kv.clone()
-        state = torch.zeros(4, dtype=torch.int32, device=dev)
+        state = torch.zeros(8, dtype=torch.int32, device=dev)
         F_.evict_plan_past(roles, n_tokens, C, SW, rank, base, sg, sl, state)
         self._plan = (('past', n_tokens), rank, base, sg, sl, state, F_.read_word_async(state))
 
@@ -311,7 +362,7 @@ class NAtSChunkLayerCache:
         rank = torch.empty(self.bsz, self.n_msks, nc, dtype=torch.int32, device=dev)
         sg = torch.empty(self.bsz, self.n_msks, dtype=torch.long, device=dev)
         sl = torch.empty_like(sg)
-        state = torch.zeros(4, dtype=torch.int32, device=dev)
+        state = torch.zeros(8, dtype=torch.int32, device=dev)
         F_.evict_plan(roles, N, C, SW, rank, sg, sl, state)
         self._plan = (N, rank, sg, sl, state, F_.read_word_async(state))
 

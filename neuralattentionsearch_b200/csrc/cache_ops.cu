@@ -403,6 +403,7 @@ struct PlaceParams {
     uint8_t* ck; uint8_t* cv; uint8_t* valid;
     long long* size_global; long long* size_local; int32_t* state;
     int C, SW, Lcap, rowB, tail;
+    int from_state;                               // 1: static launch -- act only if state[4] + 1 == C, ring position = state[5]
 };
 
 __global__ void __launch_bounds__(kCopyThreads) decode_place_kernel(const PlaceParams p) {
@@ -412,6 +413,11 @@ __global__ void __launch_bounds__(kCopyThreads) decode_place_kernel(const PlaceP
     uint8_t* ck = p.ck + (size_t)bh * p.Lcap * p.rowB;
     uint8_t* cv = p.cv + (size_t)bh * p.Lcap * p.rowB;
     uint8_t* valid = p.valid + (size_t)bh * p.Lcap;
+    int tail = p.tail;
+    if (p.from_state) {
+        if (p.state[4] + 1 != p.C) return;        // the step did not complete a chunk (uniform for the grid)
+        tail = p.state[5];
+    }
     const int role = p.roles[bh];
     const int T0 = p.state[0];
     const long long sg = p.size_global[bh], sl = p.size_local[bh];
@@ -427,7 +433,7 @@ __global__ void __launch_bounds__(kCopyThreads) decode_place_kernel(const PlaceP
         for (int i = trow; i < p.C; i += tpp) {
             const size_t src = (size_t)(T0 + i) * p.rowB + tvec;
             const uint4 kk = ld16(ck + src), vv = ld16(cv + src);
-            const int slot = (p.tail + i) % p.SW;
+            const int slot = (tail + i) % p.SW;
             const size_t rdst = (size_t)slot * p.rowB + tvec;
             const bool sw = role == NATS_ROLE_SLIDING;
             st16(ck + rdst, sw ? kk : zero);
@@ -641,6 +647,36 @@ extern "C" __attribute__((visibility("default"))) int nats_b200_cache_append(
     return NATS_OK;
 }
 
+// One thread: the step counters of the static decode step.  state[4] = tokens in the unfinished chunk, state[5] = ring
+// write position.  Runs behind the (conditional) placement kernel of the same step.
+__global__ void decode_step_advance_kernel(int32_t* state, int C, int SW) {
+    if (threadIdx.x != 0 || blockIdx.x != 0) return;
+    const int fill = state[4] + 1;
+    if (fill == C) {
+        state[4] = 0;
+        state[5] = (state[5] + C) % SW;
+    } else {
+        state[4] = fill;
+    }
+}
+
+extern "C" __attribute__((visibility("default"))) int nats_b200_decode_step_place(const uint8_t* d_roles, void* d_cache_k, void* d_cache_v, uint8_t* d_valid, int Lcap,
+                                                                       int64_t* d_size_global, int64_t* d_size_local, int32_t* d_state,
+                                                                       int B, int Hkv, int D, int C, int SW, void* stream) {
+    if (int rc = check_common(B, Hkv, 1, C, SW)) return rc;
+    if (int rc = check_row(D)) return rc;
+    NATS_CHECK_ARG(d_roles && d_cache_k && d_cache_v && d_valid && d_size_global && d_size_local && d_state, "null pointer");
+    PlaceParams p;
+    p.roles = d_roles; p.ck = (uint8_t*)d_cache_k; p.cv = (uint8_t*)d_cache_v; p.valid = d_valid;
+    p.size_global = (long long*)d_size_global; p.size_local = (long long*)d_size_local; p.state = d_state;
+    p.C = C; p.SW = SW; p.Lcap = Lcap; p.rowB = D * 2; p.tail = 0; p.from_state = 1;
+    decode_place_kernel<<<B * Hkv, kCopyThreads, 0, (cudaStream_t)stream>>>(p);
+    NATS_CHECK_CUDA(cudaGetLastError());
+    decode_step_advance_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(d_state, C, SW);
+    NATS_CHECK_CUDA(cudaGetLastError());
+    return NATS_OK;
+}
+
 extern "C" __attribute__((visibility("default"))) int nats_b200_decode_place(const uint8_t* d_roles, void* d_cache_k, void* d_cache_v, uint8_t* d_valid, int Lcap,
                                       int64_t* d_size_global, int64_t* d_size_local, int32_t* d_state,
                                       int tail, int B, int Hkv, int D, int C, int SW, void* stream) {
@@ -651,7 +687,7 @@ extern "C" __attribute__((visibility("default"))) int nats_b200_decode_place(con
     PlaceParams p;
     p.roles = d_roles; p.ck = (uint8_t*)d_cache_k; p.cv = (uint8_t*)d_cache_v; p.valid = d_valid;
     p.size_global = (long long*)d_size_global; p.size_local = (long long*)d_size_local; p.state = d_state;
-    p.C = C; p.SW = SW; p.Lcap = Lcap; p.rowB = D * 2; p.tail = tail;
+    p.C = C; p.SW = SW; p.Lcap = Lcap; p.rowB = D * 2; p.tail = tail; p.from_state = 0;
     decode_place_kernel<<<B * Hkv, kCopyThreads, 0, (cudaStream_t)stream>>>(p);
     NATS_CHECK_CUDA(cudaGetLastError());
     return NATS_OK;

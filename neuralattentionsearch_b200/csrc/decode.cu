@@ -41,6 +41,7 @@ struct DecodeParams {
     int32_t* counters;             // [B*Hkv]   (workspace)
     float* partials;               // [B*Hkv, max_splits, nrep, D+2]   (workspace)
     int Hq, Hkv, nrep, Lcap, SW, fill, max_splits;
+    int fill_from_state;           // 1: the number of tokens in the unfinished chunk is read from state[4] (static launches)
     float scale_log2;              // sm_scale * log2(e)
 };
 
@@ -94,7 +95,8 @@ __global__ void __launch_bounds__(kDecThreads) decode_kernel(const DecodeParams 
     const int nrep = p.nrep;
     const int len = (int)(p.size_global[bh] + p.size_local[bh]);
     const int T0 = p.state[0];
-    const int Ltot = len + p.fill + 1;
+    const int fill = p.fill_from_state ? p.state[4] : p.fill;
+    const int Ltot = len + fill + 1;
     const int nsplit = (Ltot + kSeg - 1) / kSeg;
     if (seg >= nsplit) return;
     const int r0 = seg * kSeg, r1 = min(Ltot, r0 + kSeg);
@@ -119,10 +121,10 @@ __global__ void __launch_bounds__(kDecThreads) decode_kernel(const DecodeParams 
     }
     // the block that owns the last logical token appends it (nobody reads that cache row in this launch)
     if (r1 == Ltot && warp == 0 && lane < CHUNKS) {
-        const size_t dst = ((size_t)bh * p.Lcap + T0 + p.fill) * D + lane * 8;
+        const size_t dst = ((size_t)bh * p.Lcap + T0 + fill) * D + lane * 8;
         st16(p.ck + dst, ld16(kn + lane * 8));
         st16(p.cv + dst, ld16(vn + lane * 8));
-        if (lane == 0) p.valid[(size_t)bh * p.Lcap + T0 + p.fill] = 1;
+        if (lane == 0) p.valid[(size_t)bh * p.Lcap + T0 + fill] = 1;
     }
     // Q as A fragments (rows = query heads of the group, 16 dims per k-step); rows >= nrep and rows 8..15 are zero
     const int hrow = lane >> 2, quad = lane & 3;
@@ -170,7 +172,7 @@ __global__ void __launch_bounds__(kDecThreads) decode_kernel(const DecodeParams 
                 const __nv_bfloat16 *kp = ck, *vp = cv;
                 if (ok) {
                     if (i < len) { kp = ck + (size_t)i * D; vp = cv + (size_t)i * D; }
-                    else if (i < len + p.fill) { const size_t ph = (size_t)(T0 + (i - len)); kp = ck + ph * D; vp = cv + ph * D; }
+                    else if (i < len + fill) { const size_t ph = (size_t)(T0 + (i - len)); kp = ck + ph * D; vp = cv + ph * D; }
                     else { kp = kn; vp = vn; }
                 }
                 const uint32_t off = r * ROWB + ((c ^ (r & 7)) << 4);
@@ -350,12 +352,12 @@ extern "C" __attribute__((visibility("default"))) size_t nats_b200_decode_worksp
            (size_t)B * Hkv * decode_max_splits(max_len) * nrep * (D + 2) * sizeof(float);
 }
 
-extern "C" __attribute__((visibility("default"))) int nats_b200_decode_fwd(const void* d_q, const void* d_k_new, const void* d_v_new, void* d_o,
-                                    void* d_cache_k, void* d_cache_v, uint8_t* d_valid, int Lcap,
-                                    const int64_t* d_size_global, const int64_t* d_size_local, const int32_t* d_state,
-                                    int fill, int max_len_bound,
-                                    int B, int Hq, int Hkv, int D, int C, int SW, float sm_scale,
-                                    void* d_workspace, size_t workspace_bytes, void* stream) {
+static int decode_impl(const void* d_q, const void* d_k_new, const void* d_v_new, void* d_o,
+                       void* d_cache_k, void* d_cache_v, uint8_t* d_valid, int Lcap,
+                       const int64_t* d_size_global, const int64_t* d_size_local, const int32_t* d_state,
+                       int fill, int max_len_bound, int fill_from_state,
+                       int B, int Hq, int Hkv, int D, int C, int SW, float sm_scale,
+                       void* d_workspace, size_t workspace_bytes, void* stream) {
     NATS_CHECK_ARG(B > 0 && Hq > 0 && Hkv > 0 && Hq % Hkv == 0, "bad head counts B=%d Hq=%d Hkv=%d", B, Hq, Hkv);
     NATS_CHECK_ARG(C > 0 && SW > 0 && SW % C == 0, "sliding window %d must be a positive multiple of the chunk size %d", SW, C);
     NATS_CHECK_ARG(d_q && d_k_new && d_v_new && d_o && d_cache_k && d_cache_v && d_valid && d_size_global && d_size_local &&
@@ -379,11 +381,31 @@ extern "C" __attribute__((visibility("default"))) int nats_b200_decode_fwd(const
     p.size_global = (const long long*)d_size_global; p.size_local = (const long long*)d_size_local; p.state = d_state;
     p.counters = (int32_t*)d_workspace;
     p.partials = (float*)((uint8_t*)d_workspace + decode_counter_bytes(B, Hkv));
-    p.Hq = Hq; p.Hkv = Hkv; p.nrep = nrep; p.Lcap = Lcap; p.SW = SW; p.fill = fill;
+    p.Hq = Hq; p.Hkv = Hkv; p.nrep = nrep; p.Lcap = Lcap; p.SW = SW; p.fill = fill; p.fill_from_state = fill_from_state;
     p.max_splits = decode_max_splits(max_len);
     p.scale_log2 = sm_scale * 1.4426950408889634f;
     dim3 grid(cdiv(max_len_bound + fill + 1, kSeg), Hkv, B);
     cudaError_t e = (D == 64) ? launch_decode<64>(p, grid, (cudaStream_t)stream) : launch_decode<128>(p, grid, (cudaStream_t)stream);
     NATS_CHECK_CUDA(e);
     return NATS_OK;
+}
+
+extern "C" __attribute__((visibility("default"))) int nats_b200_decode_fwd(const void* d_q, const void* d_k_new, const void* d_v_new, void* d_o,
+                                    void* d_cache_k, void* d_cache_v, uint8_t* d_valid, int Lcap,
+                                    const int64_t* d_size_global, const int64_t* d_size_local, const int32_t* d_state,
+                                    int fill, int max_len_bound,
+                                    int B, int Hq, int Hkv, int D, int C, int SW, float sm_scale,
+                                    void* d_workspace, size_t workspace_bytes, void* stream) {
+    return decode_impl(d_q, d_k_new, d_v_new, d_o, d_cache_k, d_cache_v, d_valid, Lcap, d_size_global, d_size_local, d_state,
+                       fill, max_len_bound, 0, B, Hq, Hkv, D, C, SW, sm_scale, d_workspace, workspace_bytes, stream);
+}
+
+extern "C" __attribute__((visibility("default"))) int nats_b200_decode_step_fwd(const void* d_q, const void* d_k_new, const void* d_v_new, void* d_o,
+                                         void* d_cache_k, void* d_cache_v, uint8_t* d_valid, int Lcap,
+                                         const int64_t* d_size_global, const int64_t* d_size_local, const int32_t* d_state,
+                                         int max_len_bound, int B, int Hq, int Hkv, int D, int C, int SW, float sm_scale,
+                                         void* d_workspace, size_t workspace_bytes, void* stream) {
+    // the fill is read on the device: size everything for the largest one
+    return decode_impl(d_q, d_k_new, d_v_new, d_o, d_cache_k, d_cache_v, d_valid, Lcap, d_size_global, d_size_local, d_state,
+                       C - 1, max_len_bound, 1, B, Hq, Hkv, D, C, SW, sm_scale, d_workspace, workspace_bytes, stream);
 }

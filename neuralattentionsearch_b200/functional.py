@@ -471,6 +471,25 @@ def decode_fwd(q: torch.Tensor, k_new: torch.Tensor, v_new: torch.Tensor, o: tor
               chunk_size, sliding_window, float(sm_scale), _p(workspace), workspace.numel(), _stream(q.device))
 
 
+def decode_step_fwd(q: torch.Tensor, k_new: torch.Tensor, v_new: torch.Tensor, o: torch.Tensor, cache_k: torch.Tensor,
+                    cache_v: torch.Tensor, valid: torch.Tensor, size_global: torch.Tensor, size_local: torch.Tensor,
+                    state: torch.Tensor, max_len_bound: int, chunk_size: int, sliding_window: int, sm_scale: float,
+                    workspace: torch.Tensor) -> None:
+    B, Hq, _, D = q.shape
+    Hkv = k_new.shape[1]
+    _lib.call('nats_b200_decode_step_fwd', _p(q), _p(k_new), _p(v_new), _p(o), _p(cache_k), _p(cache_v), _p(valid),
+              cache_k.shape[2], _p(size_global), _p(size_local), _p(state), max_len_bound, B, Hq, Hkv, D, chunk_size,
+              sliding_window, float(sm_scale), _p(workspace), workspace.numel(), _stream(q.device))
+
+
+def decode_step_place(roles: torch.Tensor, cache_k: torch.Tensor, cache_v: torch.Tensor, valid: torch.Tensor,
+                      size_global: torch.Tensor, size_local: torch.Tensor, state: torch.Tensor, chunk_size: int,
+                      sliding_window: int) -> None:
+    B, H, _, D = cache_k.shape
+    _lib.call('nats_b200_decode_step_place', _p(roles), _p(cache_k), _p(cache_v), _p(valid), cache_k.shape[2], _p(size_global),
+              _p(size_local), _p(state), B, H, D, chunk_size, sliding_window, _stream(cache_k.device))
+
+
 def decode_place(roles: torch.Tensor, cache_k: torch.Tensor, cache_v: torch.Tensor, valid: torch.Tensor,
                  size_global: torch.Tensor, size_local: torch.Tensor, state: torch.Tensor, tail: int, chunk_size: int,
                  sliding_window: int) -> None:

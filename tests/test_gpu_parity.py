@@ -716,3 +716,64 @@ def test_interleaved_caches_keep_their_own_planned_sizes():
     for lc, st, c in reversed(live):
         lc.post_update(c['N'])
         compare_cache(lc, st)
+
+
+def test_static_decode_step_equals_the_regular_one_and_replays_from_a_cuda_graph():
+    """The decode step with static launch parameters: same outputs and cache as update / decode_attention / post_update,
+    called directly and replayed from a CUDA graph that recorded it once."""
+    from neuralattentionsearch_b200 import check_status
+    B, Hq, Hkv, N, D, C, SW, steps = 2, 8, 2, 700, 128, 16, 64, 45
+    case = dict(B=B, Hkv=Hkv, SW=SW, C=C)
+    roles = orc.make_roles(B, Hkv, -(-N // C), 0.1, 0.3, seed=21)
+    roles[..., -1] = 0
+    _, k, v = inputs(B, Hq, Hkv, N, D, seed=22)
+    sts = make_steps(B, Hq, Hkv, D, steps, seed=23)
+    qs = [bf16_round(s[0]).to(dev()).bfloat16() for s in sts]
+    ks = [bf16_round(s[1]).to(dev()).bfloat16() for s in sts]
+    vs = [bf16_round(s[2]).to(dev()).bfloat16() for s in sts]
+    rs = [torch.from_numpy(s[3]).to(dev()) for s in sts]
+    # regular path
+    ref_lc = run_gpu_cache(case, roles, k, v)
+    ref_out = []
+    for i in range(steps):
+        done = ref_lc.chunk_fill_size + 1 == C
+        info = rs[i][..., None] if done else torch.zeros(B, Hkv, 1, dtype=torch.uint8, device=dev())
+        ref_lc.update(ks[i], vs[i], info, fused=True)
+        ref_out.append(ref_lc.decode_attention(qs[i]))
+        ref_lc.post_update(1)
+    # static path, called step by step
+    lc = run_gpu_cache(case, roles, k, v)
+    lc.prepare_static_decode(steps, Hq, D)
+    out = torch.empty(B, Hq, 1, D, dtype=torch.bfloat16, device=dev())
+    for i in range(steps):
+        lc.decode_step_static(qs[i], ks[i], vs[i], rs[i], out)
+        assert torch.equal(out, ref_out[i]), i
+    check_status(dev())
+    for a, b in ((lc.size_global_kv, ref_lc.size_global_kv), (lc.size_local_kv, ref_lc.size_local_kv)):
+        assert torch.equal(a, b)
+    assert (lc.n_ctx_data, lc.chunk_fill_size, lc.sliding_queue_tail) == (ref_lc.n_ctx_data, ref_lc.chunk_fill_size, ref_lc.sliding_queue_tail)
+    n = lc.n_ctx_data
+    assert torch.equal(lc.cache_k[:, :, :n], ref_lc.cache_k[:, :, :n]) and torch.equal(lc.valid_tokens[:, :, :n], ref_lc.valid_tokens[:, :, :n])
+    # static path, recorded once and replayed
+    lc = run_gpu_cache(case, roles, k, v)
+    lc.prepare_static_decode(steps + 1, Hq, D)
+    sq, sk, sv, sr = torch.empty_like(qs[0]), torch.empty_like(ks[0]), torch.empty_like(vs[0]), torch.empty_like(rs[0])
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):                       # one warm-up step outside the graph, as graph capture asks
+        sq.copy_(qs[0]); sk.copy_(ks[0]); sv.copy_(vs[0]); sr.copy_(rs[0])
+        lc.decode_step_static(sq, sk, sv, sr, out)
+    torch.cuda.current_stream().wait_stream(side)
+    assert torch.equal(out, ref_out[0])
+    graph = torch.cuda.CUDAGraph()
+    sq.copy_(qs[1]); sk.copy_(ks[1]); sv.copy_(vs[1]); sr.copy_(rs[1])
+    with torch.cuda.graph(graph):
+        lc.decode_step_static(sq, sk, sv, sr, out, recording=True)       # captured, not run
+    for i in range(1, steps):
+        sq.copy_(qs[i]); sk.copy_(ks[i]); sv.copy_(vs[i]); sr.copy_(rs[i])
+        graph.replay()
+        lc.note_static_steps(1)
+        assert torch.equal(out, ref_out[i]), i
+    check_status(dev())
+    assert torch.equal(lc.size_global_kv, ref_lc.size_global_kv) and torch.equal(lc.size_local_kv, ref_lc.size_local_kv)
+    assert (lc.n_ctx_data, lc.chunk_fill_size, lc.sliding_queue_tail) == (ref_lc.n_ctx_data, ref_lc.chunk_fill_size, ref_lc.sliding_queue_tail)
