@@ -364,7 +364,10 @@ class ChunkCacheOracle:
         C, B, H = self.C, self.B, self.H
         roles = self.roles
         Nc = roles.shape[-1]
-        if (roles == ROLE_LOCAL).all():                             # :747-749
+        # The reference returns early when every chunk of every head is local (:747-749): nothing is moved.  That is
+        # only right while every head is as long as the longest one (a first call); in a later call a shorter head would
+        # keep its new tokens behind the gap.  The early exit is taken where it is right, the general path otherwise.
+        if (roles == ROLE_LOCAL).all() and ((self.size_global + self.size_local) == self.n_ctx_data // C * C).all():
             return 0
         is_g = roles == ROLE_GLOBAL
         n_g = is_g.sum(-1)
