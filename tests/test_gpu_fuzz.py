@@ -81,3 +81,33 @@ def test_random_walk_matches_oracle(seed):
         assert_close_attn(o, ref, f'{c}: call {ci} ({n} tokens at {pos})')
         compare_cache(lc, st)
         pos += n
+
+
+@pytest.mark.parametrize('seed', range(300, 330))
+def test_random_first_call_shapes(seed):
+    """Random shapes of a first call: sequence lengths that are no multiple of anything, every group size up to 8, both
+    head dims, chunk sizes from 1 to 256 with windows of 1 to 8 chunks, random role mixes: outputs, kept-tile counts and the
+    backward statistics against the oracle."""
+    from neuralattentionsearch_b200 import check_status
+    from neuralattentionsearch_b200.functional import nats_chunk_attention_fwd
+    rng = np.random.default_rng(seed)
+    D = int(rng.choice([64, 128]))
+    C = int(rng.choice([1, 2, 8, 16, 32, 64, 128, 256]))
+    SW = C * int(rng.choice([1, 2, 4, 8]))
+    Hkv = int(rng.choice([1, 2]))
+    nrep = int(rng.integers(1, 9))
+    B = int(rng.choice([1, 2]))
+    N = int(rng.integers(1, 1500))
+    pg, pl = [(0.1, 0.3), (0.02, 0.1), (0.3, 0.3), (0.6, 0.2), (0.001, 0.001)][int(rng.integers(0, 5))]
+    roles = orc.make_roles(B, Hkv, -(-N // C), pg, pl, seed)
+    g = torch.Generator().manual_seed(seed)
+    q, k, v = (bf16_round(torch.randn(B, h, N, D, generator=g)) for h in (Hkv * nrep, Hkv, Hkv))
+    qd, kd, vd = (t.to(dev()).bfloat16() for t in (q, k, v))
+    o, lse, cnt = nats_chunk_attention_fwd(qd, kd, vd, orc.onehot_from_roles(roles).to(dev()), None, True, D ** -0.5, C,
+                                           n_rep=nrep, local_seq_max_length=SW)
+    check_status(dev())
+    what = f'B{B} Hq{Hkv * nrep} Hkv{Hkv} N{N} D{D} C{C} SW{SW}'
+    assert_close_attn(o, orc.prefill_attention(q, k, v, roles, C, SW), what)
+    lse_ref, cnt_ref = orc.prefill_stats(q, k, roles, C, SW)
+    assert np.array_equal(cnt.cpu().numpy(), cnt_ref), what
+    assert (lse.cpu() - lse_ref).abs().max().item() < 2e-2, what
