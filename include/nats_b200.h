@@ -224,7 +224,7 @@ size_t nats_b200_decode_workspace_bytes(int B, int Hq, int Hkv, int D, int max_l
  *   d_state[0] = T0;  fill = tokens already in the unfinished chunk (host knows it);  T0+fill < Lcap
  *   max_len_bound: host upper bound of T0 (sizes the grid; no host sync needed)
  *   d_workspace: nats_b200_decode_workspace_bytes(B,Hq,Hkv,D,max_len_bound+C) bytes; must be zero on first use
- *   (the kernel leaves its counters zero again);  D in {64,128};  Hq/Hkv in {1,2,4,8}
+ *   (the kernel leaves its counters zero again);  D in {64,128};  Hq/Hkv from 1 to 8
  */
 int nats_b200_decode_fwd(const void* d_q, const void* d_k_new, const void* d_v_new, void* d_o,
                          void* d_cache_k, void* d_cache_v, uint8_t* d_valid, int Lcap,

@@ -485,7 +485,7 @@ extern "C" __attribute__((visibility("default"))) const char* nats_b200_last_err
 
 extern "C" __attribute__((visibility("default"))) const char* nats_b200_build_info(void) {
     return "libnats_b200 sm_100a; prefill tile 128x128 (tcgen05/TMEM/TMA), head_dim {64,128}, N <= 524288; "
-           "decode head_dim {64,128}, group size {1,2,4,8}";
+           "decode head_dim {64,128}, group size 1..8";
 }
 
 static int check_common(int B, int Hkv, int N, int C, int SW) {
