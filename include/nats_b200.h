@@ -115,7 +115,8 @@ int nats_b200_prefill_fwd_static(const void* d_q, const void* d_k, const void* d
  * (src/nats/components/cache/nats_chunk_layer_cache.py:715-868) and the size bookkeeping of _post_update (:352-358).
  * Kept chunks of a (b,kv-head), in order: every global chunk, then the local chunks after the last global one;
  * an unfinished last chunk (N % C != 0) is never kept.
- *   d_rank         int32 [B,Hkv,Nc]  (out) destination chunk slot counted from the end of the ring, or -1
+ *   d_rank         int32 [B,Hkv,Nc]  (out) destination chunk slot counted from the end of the ring; negative for a chunk
+ *                                    that is not kept: -1 - (number of kept chunks in front of it)
  *   d_size_global  int64 [B,Hkv]     (out) SW + C * #global
  *   d_size_local   int64 [B,Hkv]     (out) C * #(local after the last global)
  *   d_state        int32 [4]         (in/out) cache state words, all zero before the first call:
@@ -186,7 +187,8 @@ int nats_b200_prefill_past_fwd(const void* d_q, const void* d_cache_k, const voi
 
 /* Step 2 -- keep-set of the call's n_tokens = fill + x_len tokens (get_updated_cache_info :715-868 with a non-empty cache).
  * A global chunk among the completed chunks drops the kept locals in front of it.
- *   d_rank int32 [B,Hkv,ceil(n_tokens/C)] (out): destination slot of a kept chunk counted from d_base, or -1
+ *   d_rank int32 [B,Hkv,ceil(n_tokens/C)] (out): destination slot of a kept chunk counted from d_base, negative otherwise
+ *                                          (encoded as for nats_b200_evict_plan)
  *   d_base int32 [B,Hkv] (out): chunk slot (position / C) the first kept chunk goes to = what the cache keeps from before
  *   d_size_global / d_size_local (in/out);  d_state as in nats_b200_evict_plan
  */

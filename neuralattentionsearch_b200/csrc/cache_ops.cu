@@ -230,7 +230,10 @@ evict_plan_kernel(const uint8_t* __restrict__ roles, int Nc, int n_full, int C, 
         __syncthreads();
         int before = s_base;
         for (int w = 0; w < warp; ++w) before += s_warp[w];
-        if (c < Nc) rank[c] = keep ? before + __popc(m & ((1u << lane) - 1u)) : -1;
+        // kept chunk: its rank; other chunks: -1 - (kept chunks in front of it), so that the number of kept chunks up to any
+        // index can be read off without a scan (the compaction finds the chunk of a given rank by bisection)
+        const int kept_before = before + __popc(m & ((1u << lane) - 1u));
+        if (c < Nc) rank[c] = keep ? kept_before : -1 - kept_before;
         __syncthreads();
         if (tid == 0) {
             int tot = 0;
@@ -269,7 +272,7 @@ struct CompactParams {
     uint8_t* ck; uint8_t* cv; uint8_t* valid;    // [BH, Lcap, rowB], [BH, Lcap]
     long long src_stride;                        // rows per head of the source
     int src_off, tail, N, Nc, n_full, C, SW, Lcap, rowB;        // rowB = D * 2 bytes; N = tokens of the call
-    int nA, nB;                                  // blocks in sections A (source tokens) and B (ring)
+    int nB;                                      // blocks of the ring section
 };
 
 __global__ void __launch_bounds__(kCopyThreads) evict_compact_kernel(const CompactParams p) {
@@ -289,23 +292,6 @@ __global__ void __launch_bounds__(kCopyThreads) evict_compact_kernel(const Compa
     const uint4 zero = make_uint4(0, 0, 0, 0);
     int blk = blockIdx.x;
     if (trow >= tpp) return;                              // head dims whose vector count does not divide 256
-    if (blk < p.nA) {
-        // section A: source-driven copy of kept chunks
-        const int t0 = blk * kTokPerBlock;
-        for (int i = trow; i < kTokPerBlock; i += tpp) {
-            const int t = t0 + i;
-            if (t >= p.n_full * p.C) break;
-            const int c = t / p.C;
-            const int r = rank[c];
-            if (r < 0) continue;
-            const size_t dst = ((size_t)(base + r) * p.C + (t - c * p.C)) * p.rowB + tvec;
-            const size_t src = (size_t)(p.src_off + t) * p.rowB + tvec;
-            st16(ck + dst, ld16_stream(k + src));
-            st16(cv + dst, ld16_stream(v + src));
-        }
-        return;
-    }
-    blk -= p.nA;
     if (blk < p.nB) {
         // section B: the last min(n_full, SW/C) complete chunks of the call go to the ring slots behind the tail (data if
         // the chunk is a sliding one, else zeros + invalid); slots the call does not reach keep what they held
@@ -337,8 +323,10 @@ __global__ void __launch_bounds__(kCopyThreads) evict_compact_kernel(const Compa
         return;
     }
     blk -= p.nB;
-    // section C: destination-driven.  [SW, base*C) = what the cache kept from before this call; [base*C, len) is written by
-    // section A; [len, Lcap) is zero except the tokens of the unfinished chunk at [T0, T0+rem)
+    // main region, destination-driven.  [SW, base*C) = what the cache kept from before this call; [base*C, len) = the kept
+    // chunks of this call (slot r holds the chunk whose rank is r: ranks grow with the chunk index, so the chunk is found
+    // by bisection); [len, Lcap) is zero except the tokens of the unfinished chunk at [T0, T0+rem).  Launching blocks per
+    // destination instead of per source token matters: most source chunks are not kept.
     const int len = (int)(p.size_global[bh] + p.size_local[bh]);
     const int T0 = p.state[0];
     const int rem = p.N - p.n_full * p.C;
@@ -350,10 +338,25 @@ __global__ void __launch_bounds__(kCopyThreads) evict_compact_kernel(const Compa
         if (tvec == 0) valid[d] = (d < len || in_tail) ? 1 : 0;
         const size_t dst = (size_t)d * p.rowB + tvec;
         if (d < len) {
-            if (past && d < base * p.C) {
-                st16(ck + dst, ld16_stream(k + dst));
-                st16(cv + dst, ld16_stream(v + dst));
+            if (d < base * p.C) {
+                if (past) {
+                    st16(ck + dst, ld16_stream(k + dst));
+                    st16(cv + dst, ld16_stream(v + dst));
+                }
+                continue;
             }
+            // the chunk of rank r: the smallest index up to which r + 1 chunks are kept
+            const int r = d / p.C - base;
+            int lo = r, hi = p.n_full - 1;                 // it cannot sit in front of index r
+            while (lo < hi) {
+                const int mid = (lo + hi) >> 1;
+                const int v = rank[mid];
+                const int kept_upto = v >= 0 ? v + 1 : -1 - v;         // kept chunks in [0, mid]
+                if (kept_upto >= r + 1) hi = mid; else lo = mid + 1;
+            }
+            const size_t src = (size_t)(p.src_off + lo * p.C + d % p.C) * p.rowB + tvec;
+            st16(ck + dst, ld16_stream(k + src));
+            st16(cv + dst, ld16_stream(v + src));
             continue;
         }
         if (in_tail) {
@@ -587,10 +590,9 @@ extern "C" __attribute__((visibility("default"))) int nats_b200_evict_compact(co
     p.size_global = (const long long*)d_size_global; p.size_local = (const long long*)d_size_local; p.state = d_state;
     p.ck = (uint8_t*)d_cache_k; p.cv = (uint8_t*)d_cache_v; p.valid = d_valid;
     p.N = N; p.Nc = cdiv(N, C); p.n_full = N / C; p.C = C; p.SW = SW; p.Lcap = Lcap; p.rowB = D * 2;
-    p.nA = cdiv(p.n_full * C, kTokPerBlock);
     p.nB = cdiv(SW, kTokPerBlock);
     const int nC = cdiv(Lcap - SW, kTokPerBlock);
-    dim3 grid(p.nA + p.nB + nC, B * Hkv);
+    dim3 grid(p.nB + nC, B * Hkv);
     evict_compact_kernel<<<grid, kCopyThreads, 0, (cudaStream_t)stream>>>(p);
     NATS_CHECK_CUDA(cudaGetLastError());
     return NATS_OK;
@@ -619,10 +621,9 @@ extern "C" __attribute__((visibility("default"))) int nats_b200_evict_compact_pa
     p.size_global = (const long long*)d_size_global; p.size_local = (const long long*)d_size_local; p.state = d_state;
     p.ck = (uint8_t*)d_cache_k; p.cv = (uint8_t*)d_cache_v; p.valid = d_valid;
     p.N = n_tokens; p.Nc = cdiv(n_tokens, C); p.n_full = n_tokens / C; p.C = C; p.SW = SW; p.Lcap = Lcap; p.rowB = D * 2;
-    p.nA = cdiv(p.n_full * C, kTokPerBlock);
     p.nB = cdiv(SW, kTokPerBlock);
     const int nC = cdiv(Lcap - SW, kTokPerBlock);
-    dim3 grid(p.nA + p.nB + nC, B * Hkv);
+    dim3 grid(p.nB + nC, B * Hkv);
     evict_compact_kernel<<<grid, kCopyThreads, 0, (cudaStream_t)stream>>>(p);
     NATS_CHECK_CUDA(cudaGetLastError());
     return NATS_OK;
