@@ -368,7 +368,6 @@ def main():
         evs[i][2].record()
     barrier()
     ms_total = evs[0][0].elapsed_time(evs[-1][2])
-    clocks = sampler.stop() if rank == 0 else None
     check_status(device)
     ms_prefill = float(np.mean([e[0].elapsed_time(e[1]) for e in evs]))
     ms_evict = float(np.mean([e[1].elapsed_time(e[2]) for e in evs]))
@@ -499,6 +498,10 @@ def main():
         if world > 1:      # NCCL only here: gather the last step's outputs of all ranks
             outs = [torch.empty_like(r['out']) for _ in range(world)]
             dist.all_gather(outs, r['out'])
+
+    # the clock samples cover every timed GPU leg above (the prefill + eviction steps alone last ~12 ms, less than one
+    # sampling interval of nvidia-smi)
+    clocks = sampler.stop() if rank == 0 else None
 
     # ---- CPU baseline (rank 0, single GPU run only) ----
     cpu = None
