@@ -21,7 +21,6 @@ struct RopeParams {
 constexpr int kRopeThreads = 256;
 constexpr int kRopeTokens = 8;            // tokens per block
 
-__device__ __forceinline__ float bf16_round(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
 
 // 8 bf16 values in a uint4
 struct Vec8 { float f[8]; };
@@ -45,17 +44,43 @@ __device__ __forceinline__ uint4 pack8(const Vec8& v) {
     return make_uint4(w[0], w[1], w[2], w[3]);
 }
 
+// bf16(a * b) for four packed pairs: the product of two bf16 values is exact in fp32, so one rounding either way
+__device__ __forceinline__ uint4 mul8(uint4 a, uint4 b) {
+    uint4 r;
+    const __nv_bfloat162* x = reinterpret_cast<const __nv_bfloat162*>(&a);
+    const __nv_bfloat162* y = reinterpret_cast<const __nv_bfloat162*>(&b);
+    __nv_bfloat162* z = reinterpret_cast<__nv_bfloat162*>(&r);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) z[i] = __hmul2(x[i], y[i]);
+    return r;
+}
+__device__ __forceinline__ uint4 neg8(uint4 a) {
+    return make_uint4(a.x ^ 0x80008000u, a.y ^ 0x80008000u, a.z ^ 0x80008000u, a.w ^ 0x80008000u);
+}
+// bf16(a + b), the sum taken in fp32 like the element-wise chain does
+__device__ __forceinline__ uint4 add8(uint4 a, uint4 b) {
+    const Vec8 x = unpack8(a), y = unpack8(b);
+    Vec8 o;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) o.f[i] = __fadd_rn(x.f[i], y.f[i]);
+    return pack8(o);
+}
+
+// VPH = 16-byte vectors per half head (D / 16), 0 = read it from the parameters
+template <int VPH>
 __global__ void __launch_bounds__(kRopeThreads) rope_split_heads_kernel(const RopeParams p) {
     const int b = blockIdx.y;
     const int t0 = blockIdx.x * kRopeTokens;
-    const int vph = p.D / 16;                           // 16-byte vectors per half head
+    const int vph = VPH > 0 ? VPH : p.D / 16;
     const int Ht = p.Hq + 2 * p.Hkv;
-    const int units = kRopeTokens * Ht * vph;
-    for (int u = threadIdx.x; u < units; u += kRopeThreads) {
-        const int j = u % vph;
-        const int h = (u / vph) % Ht;
-        const int t = t0 + u / (vph * Ht);
-        if (t >= p.N) break;
+    // a thread keeps its vector index j; (token, head) pairs are walked without divisions
+    const int j = threadIdx.x % vph;
+    const int pair_stride = kRopeThreads / vph;          // host side guarantees that vph divides the block
+    int h = threadIdx.x / vph, t = t0;
+    while (h >= Ht) { h -= Ht; ++t; }
+    const int t_end = min(t0 + kRopeTokens, p.N);
+    const int lo = j * 8, hi = p.D / 2 + j * 8;
+    while (t < t_end) {
         const __nv_bfloat16* in;
         __nv_bfloat16* out;
         bool rotate = true;
@@ -72,27 +97,20 @@ __global__ void __launch_bounds__(kRopeThreads) rope_split_heads_kernel(const Ro
             out = p.v_out + (((size_t)b * p.Hkv + hv) * p.N + t) * p.D;
             rotate = false;
         }
-        const int lo = j * 8, hi = p.D / 2 + j * 8;
-        const uint4 r1 = ld16_stream(in + lo), r2 = ld16_stream(in + hi);
+        const uint4 x1 = ld16_stream(in + lo), x2 = ld16_stream(in + hi);
         if (!rotate) {
-            st16(out + lo, r1);
-            st16(out + hi, r2);
-            continue;
-        }
-        const __nv_bfloat16* cs = p.cos + (size_t)b * p.cs_batch + (size_t)t * p.D;
-        const __nv_bfloat16* sn = p.sin + (size_t)b * p.cs_batch + (size_t)t * p.D;
-        const Vec8 x1 = unpack8(r1), x2 = unpack8(r2);
-        const Vec8 c1 = unpack8(ld16(cs + lo)), c2 = unpack8(ld16(cs + hi));
-        const Vec8 s1 = unpack8(ld16(sn + lo)), s2 = unpack8(ld16(sn + hi));
-        Vec8 o1, o2;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
+            st16(out + lo, x1);
+            st16(out + hi, x2);
+        } else {
+            const __nv_bfloat16* cs = p.cos + (size_t)b * p.cs_batch + (size_t)t * p.D;
+            const __nv_bfloat16* sn = p.sin + (size_t)b * p.cs_batch + (size_t)t * p.D;
+            const uint4 c1 = ld16(cs + lo), c2 = ld16(cs + hi), s1 = ld16(sn + lo), s2 = ld16(sn + hi);
             // first half: x1 * cos - x2 * sin; second half: x2 * cos + x1 * sin (rotate_half = [-x2, x1])
-            o1.f[i] = bf16_round(__fmul_rn(x1.f[i], c1.f[i])) + bf16_round(__fmul_rn(-x2.f[i], s1.f[i]));
-            o2.f[i] = bf16_round(__fmul_rn(x2.f[i], c2.f[i])) + bf16_round(__fmul_rn(x1.f[i], s2.f[i]));
+            st16(out + lo, add8(mul8(x1, c1), mul8(neg8(x2), s1)));
+            st16(out + hi, add8(mul8(x2, c2), mul8(x1, s2)));
         }
-        st16(out + lo, pack8(o1));
-        st16(out + hi, pack8(o2));
+        h += pair_stride;
+        while (h >= Ht) { h -= Ht; ++t; }
     }
 }
 
@@ -120,7 +138,10 @@ extern "C" __attribute__((visibility("default"))) int nats_b200_rope_split_heads
     p.q_out = (__nv_bfloat16*)d_q_out; p.k_out = (__nv_bfloat16*)d_k_out; p.v_out = (__nv_bfloat16*)d_v_out;
     p.B = B; p.N = N; p.Hq = Hq; p.Hkv = Hkv; p.D = D;
     dim3 grid(cdiv(N, kRopeTokens), B);
-    rope_split_heads_kernel<<<grid, kRopeThreads, 0, (cudaStream_t)stream>>>(p);
+    NATS_CHECK_ARG(kRopeThreads % (D / 16) == 0, "head_dim %d: the vectors of a half head must divide the block of %d threads", D, kRopeThreads);
+    if (D == 128) rope_split_heads_kernel<8><<<grid, kRopeThreads, 0, (cudaStream_t)stream>>>(p);
+    else if (D == 64) rope_split_heads_kernel<4><<<grid, kRopeThreads, 0, (cudaStream_t)stream>>>(p);
+    else rope_split_heads_kernel<0><<<grid, kRopeThreads, 0, (cudaStream_t)stream>>>(p);
     NATS_CHECK_CUDA(cudaGetLastError());
     return NATS_OK;
 }
