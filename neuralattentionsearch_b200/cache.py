@@ -75,6 +75,7 @@ class NAtSChunkLayerCache:
         if self._t0_exact is None:
             self._t0_exact = int(self._state[0].item())
             self._t0_bound = self._t0_synced = self._t0_exact
+            F_.check_status(self.device)      # the host waits for the device here anyway: a failed prefill must not go unnoticed
         return self._t0_exact
 
     @property

@@ -328,11 +328,16 @@ __global__ void __launch_bounds__(kDecThreads) decode_kernel(const DecodeParams 
 template <int D>
 static cudaError_t launch_decode(const DecodeParams& p, dim3 grid, cudaStream_t st) {
     constexpr int smem = kDecWarps * kDecStages * 2 * kTileTok * D * 2;
-    static bool attr_set = false;
-    if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(decode_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    // the opt-in to more than 48 KB of dynamic shared memory is a per-device attribute of the kernel
+    constexpr int kMaxDev = 64;
+    static bool attr_set[kMaxDev] = {};
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 0 || dev >= kMaxDev || !attr_set[dev]) {
+        e = cudaFuncSetAttribute(decode_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return e;
-        attr_set = true;
+        if (dev >= 0 && dev < kMaxDev) attr_set[dev] = true;
     }
     decode_kernel<D><<<grid, kDecThreads, smem, st>>>(p);
     return cudaGetLastError();

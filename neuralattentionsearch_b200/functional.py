@@ -35,6 +35,16 @@ def _stream(device: torch.device) -> int:
     return torch.cuda.current_stream(device).cuda_stream
 
 
+def _call(device: torch.device, name: str, *args) -> None:
+    """Calls an entry point with ``device`` current: the library reads the current device for the SM count, the
+    per-device kernel attributes and its built-in scratch, while the stream belongs to the tensors' device."""
+    if device.index is not None and device.index != torch.cuda.current_device():
+        with torch.cuda.device(device):
+            _lib.call(name, *args)
+    else:
+        _lib.call(name, *args)
+
+
 def _need_cuda(*tensors: torch.Tensor) -> torch.device:
     dev = tensors[0].device
     for t in tensors:
@@ -53,14 +63,19 @@ def status_word(device: torch.device) -> torch.Tensor:
     return _status[idx]
 
 
+def _raise_status(device: torch.device, code: int) -> None:
+    status_word(device).zero_()
+    raise _lib.NatsB200Error(f'the prefill kernel gave up a bounded wait (code {code}); its output is invalid')
+
+
 def check_status(device: torch.device | None = None) -> None:
-    """Synchronises with the device and raises if a kernel reported a timed-out wait since the last check."""
+    """Synchronises with the device and raises if a kernel reported a timed-out wait since the last check.  The cache
+    classes call this wherever they read a value back from the device anyway; callers of the bare functions call it
+    before they trust an output."""
     device = torch.device('cuda', torch.cuda.current_device()) if device is None else device
-    word = status_word(device)
-    code = int(word.item())
+    code = int(status_word(device).item())
     if code != 0:
-        word.zero_()
-        raise _lib.NatsB200Error(f'nats_b200_prefill_fwd gave up a bounded wait (code {code}); its output is invalid')
+        _raise_status(device, code)
 
 
 def _workspace(kind: str, device: torch.device, nbytes: int, zero: bool = False) -> torch.Tensor:
@@ -73,7 +88,7 @@ def _workspace(kind: str, device: torch.device, nbytes: int, zero: bool = False)
 
 
 class _PinnedWords:
-    """A few pinned int32 words per device for small asynchronous read-backs.  Allocating pinned memory per call would
+    """A few pinned int32 word pairs per device for small asynchronous read-backs.  Allocating pinned memory per call would
     synchronise the device, so the words are allocated once and handed out again when their reader is done with them."""
     _free: dict = {}
     _lock = __import__('threading').Lock()
@@ -82,7 +97,7 @@ class _PinnedWords:
     def take(cls, dev: torch.device) -> torch.Tensor:
         with cls._lock:
             free = cls._free.setdefault(dev, [])
-            return free.pop() if free else torch.empty(1, dtype=torch.int32, pin_memory=True)
+            return free.pop() if free else torch.empty(2, dtype=torch.int32, pin_memory=True)
 
     @classmethod
     def give_back(cls, dev: torch.device, word: torch.Tensor) -> None:
@@ -91,20 +106,24 @@ class _PinnedWords:
 
 
 class _AsyncWord:
-    """An int32 scalar on its way from the device to the host.  Calling the object waits for the copy and returns the
-    value; the pinned word goes back to the pool when the value has been read or the object is dropped."""
+    """An int32 scalar on its way from the device to the host, with the device's prefill status word riding along.
+    Calling the object waits for the copy and returns the value (and raises if a kernel that ran before the copy had
+    given up a bounded wait); the pinned words go back to the pool when the value has been read or the object is dropped."""
 
     def __init__(self, src: torch.Tensor):
         self.dev = src.device
         self.word = _PinnedWords.take(self.dev)
-        self.word.copy_(src[:1], non_blocking=True)
+        self.word[:1].copy_(src[:1], non_blocking=True)
+        self.word[1:].copy_(status_word(self.dev), non_blocking=True)
         self.done = torch.cuda.Event()
         self.done.record(torch.cuda.current_stream(self.dev))
 
     def __call__(self) -> int:
         self.done.synchronize()
-        value = int(self.word[0])
+        value, code = int(self.word[0]), int(self.word[1])
         self._release()
+        if code != 0:
+            _raise_status(self.dev, code)
         return value
 
     def _release(self):
@@ -167,7 +186,7 @@ def prefill_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, roles: 
     nbytes = lib.nats_b200_prefill_workspace_bytes(B, Hkv, N, chunk_size)
     ws = _workspace('prefill', dev, nbytes)
     scale = (1.0 / math.sqrt(D)) if sm_scale is None else float(sm_scale)
-    _lib.call('nats_b200_prefill_fwd', _p(qb), _p(kb), _p(vb), _p(o), _p(roles.contiguous()), B, Hq, Hkv, N, D,
+    _call(dev, 'nats_b200_prefill_fwd', _p(qb), _p(kb), _p(vb), _p(o), _p(roles.contiguous()), B, Hq, Hkv, N, D,
               chunk_size, sliding_window, scale, _p(ws), ws.numel(), _p(kept_tiles), _p(status_word(dev)), _stream(dev))
     return o if q.dtype == torch.bfloat16 else o.to(q.dtype)
 
@@ -242,7 +261,7 @@ def dense_role_mask(roles: torch.Tensor, chunk_size: int, sliding_window: int, n
     nt = -(-n // 128)
     tmax = torch.empty(B, H, nt, dtype=torch.int32, device=dev)
     tmin = torch.empty_like(tmax)
-    _lib.call('nats_b200_role_prep', _p(roles.contiguous()), B, H, n, chunk_size, sliding_window, _p(lim), _p(tmax), _p(tmin),
+    _call(dev, 'nats_b200_role_prep', _p(roles.contiguous()), B, H, n, chunk_size, sliding_window, _p(lim), _p(tmax), _p(tmin),
               None, _stream(dev))
     lim_tok = lim.repeat_interleave(chunk_size, -1)[..., :n].long()
     ar = torch.arange(n, device=dev)
@@ -324,7 +343,7 @@ def nats_chunk_attention_fwd(q, k, v, seq_info, end_seqs_idx, causal, sm_scale, 
     n_vis = torch.empty(B, Hq, N, dtype=torch.int32, device=dev)
     lib = _lib.lib()
     ws = _workspace('prefill', dev, lib.nats_b200_prefill_workspace_bytes(B, Hkv, N, nats_chunk_size))
-    _lib.call('nats_b200_prefill_fwd_stats', _p(qb), _p(kb), _p(vb), _p(o), _p(roles), B, Hq, Hkv, N, D, nats_chunk_size,
+    _call(dev, 'nats_b200_prefill_fwd_stats', _p(qb), _p(kb), _p(vb), _p(o), _p(roles), B, Hq, Hkv, N, D, nats_chunk_size,
               local_seq_max_length, float(sm_scale), _p(ws), ws.numel(), None, _p(lse), _p(n_vis), _p(status_word(dev)),
               _stream(dev))
     return (o if q.dtype == torch.bfloat16 else o.to(q.dtype)), lse, n_vis
@@ -357,7 +376,7 @@ def rope_split_heads(q_in: torch.Tensor, k_in: torch.Tensor, v_in: torch.Tensor,
     q = torch.empty(B, n_heads, N, head_dim, dtype=torch.bfloat16, device=dev)
     k = torch.empty(B, n_kv_heads, N, head_dim, dtype=torch.bfloat16, device=dev)
     v = torch.empty_like(k)
-    _lib.call('nats_b200_rope_split_heads', _p(ins[0]), _p(ins[1]), _p(ins[2]), ins[0].stride(1), ins[1].stride(1),
+    _call(dev, 'nats_b200_rope_split_heads', _p(ins[0]), _p(ins[1]), _p(ins[2]), ins[0].stride(1), ins[1].stride(1),
               ins[2].stride(1), _p(cos), _p(sin), 0 if cos.numel() == N * head_dim else N * head_dim, _p(q), _p(k), _p(v),
               B, N, n_heads, n_kv_heads, head_dim, _stream(dev))
     return q, k, v
@@ -369,7 +388,7 @@ def rope_split_heads(q_in: torch.Tensor, k_in: torch.Tensor, v_in: torch.Tensor,
 def evict_plan(roles: torch.Tensor, n: int, chunk_size: int, sliding_window: int, rank: torch.Tensor,
                size_global: torch.Tensor, size_local: torch.Tensor, state: torch.Tensor) -> None:
     B, H, _ = roles.shape
-    _lib.call('nats_b200_evict_plan', _p(roles), B, H, n, chunk_size, sliding_window, _p(rank), _p(size_global),
+    _call(roles.device, 'nats_b200_evict_plan', _p(roles), B, H, n, chunk_size, sliding_window, _p(rank), _p(size_global),
               _p(size_local), _p(state), _stream(roles.device))
 
 
@@ -377,7 +396,7 @@ def evict_compact(k: torch.Tensor, v: torch.Tensor, roles: torch.Tensor, rank: t
                   size_local: torch.Tensor, state: torch.Tensor, chunk_size: int, sliding_window: int,
                   cache_k: torch.Tensor, cache_v: torch.Tensor, valid: torch.Tensor) -> None:
     B, H, N, D = k.shape
-    _lib.call('nats_b200_evict_compact', _p(k), _p(v), _p(roles), _p(rank), _p(size_global), _p(size_local), _p(state),
+    _call(k.device, 'nats_b200_evict_compact', _p(k), _p(v), _p(roles), _p(rank), _p(size_global), _p(size_local), _p(state),
               B, H, N, D, chunk_size, sliding_window, _p(cache_k), _p(cache_v), _p(valid), cache_k.shape[2],
               _stream(k.device))
 
@@ -385,7 +404,7 @@ def evict_compact(k: torch.Tensor, v: torch.Tensor, roles: torch.Tensor, rank: t
 def cache_append(k_new: torch.Tensor, v_new: torch.Tensor, cache_k: torch.Tensor, cache_v: torch.Tensor,
                  valid: torch.Tensor, pos: int) -> None:
     B, H, x_len, D = k_new.shape
-    _lib.call('nats_b200_cache_append', _p(k_new), _p(v_new), _p(cache_k), _p(cache_v), _p(valid), B, H, x_len, D,
+    _call(k_new.device, 'nats_b200_cache_append', _p(k_new), _p(v_new), _p(cache_k), _p(cache_v), _p(valid), B, H, x_len, D,
               cache_k.shape[2], pos, _stream(k_new.device))
 
 
@@ -416,7 +435,7 @@ def prefill_attention_past(q: torch.Tensor, cache_k: torch.Tensor, cache_v: torc
     nbytes = lib.nats_b200_prefill_past_workspace_bytes(B, Hkv, t0 + fill + x_len, chunk_size)
     ws = _workspace('prefill', dev, nbytes)
     scale = (1.0 / math.sqrt(D)) if sm_scale is None else float(sm_scale)
-    _lib.call('nats_b200_prefill_past_fwd', _p(qb), _p(cache_k), _p(cache_v), _p(o), _p(roles_new.contiguous()), _p(valid),
+    _call(dev, 'nats_b200_prefill_past_fwd', _p(qb), _p(cache_k), _p(cache_v), _p(o), _p(roles_new.contiguous()), _p(valid),
               valid.stride(1), _p(size_global), _p(size_local), B, Hq, Hkv, x_len, D, chunk_size, sliding_window, cap, t0, fill,
               tail, scale,
               _p(ws), ws.numel(), _p(kept_tiles), _p(status_word(dev)), _stream(dev))
@@ -434,7 +453,7 @@ def layout_row_limits(roles_new: torch.Tensor, valid: torch.Tensor, size_global:
     nt = -(-n_kv // 128)
     tmax = torch.empty(B, H, nt, dtype=torch.int32, device=dev)
     tmin = torch.empty_like(tmax)
-    _lib.call('nats_b200_role_prep_past', _p(roles_new.contiguous()), _p(valid), _p(size_global), _p(size_local), B, H, x_len,
+    _call(dev, 'nats_b200_role_prep_past', _p(roles_new.contiguous()), _p(valid), _p(size_global), _p(size_local), B, H, x_len,
               chunk_size, sliding_window, valid.stride(1), t0, fill, tail, _p(lim), _p(tmax), _p(tmin), None, _stream(dev))
     return lim
 
@@ -442,7 +461,7 @@ def layout_row_limits(roles_new: torch.Tensor, valid: torch.Tensor, size_global:
 def evict_plan_past(roles_new: torch.Tensor, n_tokens: int, chunk_size: int, sliding_window: int, rank: torch.Tensor,
                     base: torch.Tensor, size_global: torch.Tensor, size_local: torch.Tensor, state: torch.Tensor) -> None:
     B, H, _ = roles_new.shape
-    _lib.call('nats_b200_evict_plan_past', _p(roles_new), B, H, n_tokens, chunk_size, sliding_window, _p(rank), _p(base),
+    _call(roles_new.device, 'nats_b200_evict_plan_past', _p(roles_new), B, H, n_tokens, chunk_size, sliding_window, _p(rank), _p(base),
               _p(size_global), _p(size_local), _p(state), _stream(roles_new.device))
 
 
@@ -451,7 +470,7 @@ def evict_compact_past(old_k: torch.Tensor, old_v: torch.Tensor, old_valid: torc
                        state: torch.Tensor, n_tokens: int, chunk_size: int, sliding_window: int, t0_old: int, tail_old: int,
                        cache_k: torch.Tensor, cache_v: torch.Tensor, valid: torch.Tensor) -> None:
     B, H, cap_old, D = old_k.shape
-    _lib.call('nats_b200_evict_compact_past', _p(old_k), _p(old_v), _p(old_valid), cap_old, _p(roles_new), _p(rank), _p(base),
+    _call(old_k.device, 'nats_b200_evict_compact_past', _p(old_k), _p(old_v), _p(old_valid), cap_old, _p(roles_new), _p(rank), _p(base),
               _p(size_global), _p(size_local), _p(state), B, H, n_tokens, D, chunk_size, sliding_window, t0_old, tail_old,
               _p(cache_k), _p(cache_v), _p(valid), cache_k.shape[2], _stream(old_k.device))
 
@@ -466,7 +485,7 @@ def decode_fwd(q: torch.Tensor, k_new: torch.Tensor, v_new: torch.Tensor, o: tor
                sm_scale: float, workspace: torch.Tensor) -> None:
     B, Hq, _, D = q.shape
     Hkv = k_new.shape[1]
-    _lib.call('nats_b200_decode_fwd', _p(q), _p(k_new), _p(v_new), _p(o), _p(cache_k), _p(cache_v), _p(valid),
+    _call(q.device, 'nats_b200_decode_fwd', _p(q), _p(k_new), _p(v_new), _p(o), _p(cache_k), _p(cache_v), _p(valid),
               cache_k.shape[2], _p(size_global), _p(size_local), _p(state), fill, max_len_bound, B, Hq, Hkv, D,
               chunk_size, sliding_window, float(sm_scale), _p(workspace), workspace.numel(), _stream(q.device))
 
@@ -477,7 +496,7 @@ def decode_step_fwd(q: torch.Tensor, k_new: torch.Tensor, v_new: torch.Tensor, o
                     workspace: torch.Tensor) -> None:
     B, Hq, _, D = q.shape
     Hkv = k_new.shape[1]
-    _lib.call('nats_b200_decode_step_fwd', _p(q), _p(k_new), _p(v_new), _p(o), _p(cache_k), _p(cache_v), _p(valid),
+    _call(q.device, 'nats_b200_decode_step_fwd', _p(q), _p(k_new), _p(v_new), _p(o), _p(cache_k), _p(cache_v), _p(valid),
               cache_k.shape[2], _p(size_global), _p(size_local), _p(state), max_len_bound, B, Hq, Hkv, D, chunk_size,
               sliding_window, float(sm_scale), _p(workspace), workspace.numel(), _stream(q.device))
 
@@ -486,7 +505,7 @@ def decode_step_place(roles: torch.Tensor, cache_k: torch.Tensor, cache_v: torch
                       size_global: torch.Tensor, size_local: torch.Tensor, state: torch.Tensor, chunk_size: int,
                       sliding_window: int) -> None:
     B, H, _, D = cache_k.shape
-    _lib.call('nats_b200_decode_step_place', _p(roles), _p(cache_k), _p(cache_v), _p(valid), cache_k.shape[2], _p(size_global),
+    _call(cache_k.device, 'nats_b200_decode_step_place', _p(roles), _p(cache_k), _p(cache_v), _p(valid), cache_k.shape[2], _p(size_global),
               _p(size_local), _p(state), B, H, D, chunk_size, sliding_window, _stream(cache_k.device))
 
 
@@ -494,5 +513,5 @@ def decode_place(roles: torch.Tensor, cache_k: torch.Tensor, cache_v: torch.Tens
                  size_global: torch.Tensor, size_local: torch.Tensor, state: torch.Tensor, tail: int, chunk_size: int,
                  sliding_window: int) -> None:
     B, H, _, D = cache_k.shape
-    _lib.call('nats_b200_decode_place', _p(roles), _p(cache_k), _p(cache_v), _p(valid), cache_k.shape[2], _p(size_global),
+    _call(cache_k.device, 'nats_b200_decode_place', _p(roles), _p(cache_k), _p(cache_v), _p(valid), cache_k.shape[2], _p(size_global),
               _p(size_local), _p(state), tail, B, H, D, chunk_size, sliding_window, _stream(cache_k.device))

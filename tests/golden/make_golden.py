@@ -44,6 +44,9 @@ CASES = {
     'k128_gqa':       dict(B=1, Hq=4, Hkv=1, N=640, D=128, C=128, SW=256, pg=0.10, pl=0.20, seed=12, n_decode=0),
     'k64_ragged':     dict(B=2, Hq=4, Hkv=2, N=300, D=64,  C=16,  SW=64,  pg=0.10, pl=0.30, seed=13, n_decode=40),
     'k128_decode':    dict(B=2, Hq=4, Hkv=2, N=256, D=128, C=32,  SW=64,  pg=0.15, pl=0.30, seed=14, n_decode=70),
+    # the reference's own CPU-runnable configuration: one layer, batch 1, 8 heads (MHA), head_dim 64, 2048 tokens, seed 0,
+    # window 256, chunk 64, about 10 % global / 30 % local / 60 % sliding chunks
+    'cfg1_mha_2048':  dict(B=1, Hq=8, Hkv=8, N=2048, D=64, C=64,  SW=256, pg=0.10, pl=0.30, seed=0, n_decode=0),
 }
 # multi-token calls over an existing cache: the sequence is fed in the given segments (N = their sum), then decoded.
 # Shapes avoid two reference defects: a first segment shorter than one chunk followed by a multi-token call raises
@@ -67,6 +70,23 @@ TOK_CASES = {
     'tok_tiny':    dict(B=2, Hq=4, Hkv=2, N=48,  D=16, C=1, SW=16, pg=0.10, pl=0.30, seed=41, n_decode=0),
     'tok_long':    dict(B=2, Hq=2, Hkv=2, N=333, D=16, C=1, SW=32, pg=0.05, pl=0.30, seed=42, n_decode=0),
     'tok_k64':     dict(B=1, Hq=4, Hkv=2, N=512, D=64, C=1, SW=64, pg=0.05, pl=0.25, seed=43, n_decode=0),
+}
+# token-granular cache, single-token steps: the reference places tokens in batches of update_chunk_size = 16, so its
+# index-level state is comparable right after each batched update (steps 16, 32, ... after the prefill).
+TOKDEC_CASES = {
+    'tokdec_tiny': dict(B=2, Hq=4, Hkv=2, N=48, D=16, C=1, SW=16, pg=0.10, pl=0.30, seed=51, n_decode=64),
+    'tokdec_k64':  dict(B=2, Hq=4, Hkv=2, N=128, D=64, C=1, SW=32, pg=0.08, pl=0.30, seed=52, n_decode=48),
+}
+TOK_UPDATE = 16
+# role sampling (pooled hidden states -> role head -> argmax): a sequence of calls through the reference layer -- a prefill
+# that ends inside a chunk, a multi-token call that starts inside a chunk, single tokens across chunk boundaries, a call
+# that completes no chunk.  ``enh`` is the value the layer adds to the global logit (0.1 in the reference's own modules;
+# its Hugging Face forward, hf/llama_nats_chunk.py:194-215, is the same computation without it).
+ROLE_CASES = {
+    'roles_mean':    dict(B=2, Hq=4, Hkv=2, D=16, C=8, SW=32, method='mean', enh=0.1, seed=61, calls=[50, 13] + [1] * 20 + [3, 1, 1, 25, 2, 6]),
+    'roles_max':     dict(B=2, Hq=4, Hkv=2, D=16, C=8, SW=32, method='max',  enh=0.1, seed=62, calls=[50, 13] + [1] * 20 + [3, 1, 1, 25, 2, 6]),
+    'roles_mean_hf': dict(B=2, Hq=4, Hkv=2, D=16, C=8, SW=32, method='mean', enh=0.0, seed=63, calls=[64, 9] + [1] * 18 + [5, 30]),
+    'roles_max_hf':  dict(B=2, Hq=4, Hkv=2, D=16, C=4, SW=16, method='max',  enh=0.0, seed=64, calls=[30, 7] + [1] * 11 + [2, 1, 17]),
 }
 ROW_STRIDE = 5
 
@@ -151,6 +171,25 @@ def state_of(layer_cache) -> dict:
     )
 
 
+def log2_sum_exp2(q: torch.Tensor, k: torch.Tensor, mask: np.ndarray, tiny: bool) -> np.ndarray:
+    """M of the reference's training forward (triton/nats_chunk_attention.py:319-330: ``m_i + log2(l_i)``) = log2 of the
+    row's sum of exp2(score * sm_scale * log2 e) over the keys the row sees, evaluated in float64 over the reference's own
+    mask.  q and k are rounded to bf16 first, the precision the kernels take them in.  [B,Hq,N] (every ROW_STRIDE-th row
+    for the kernel-sized cases)."""
+    B, Hq, N, D = q.shape
+    Hkv = k.shape[1]
+    qd, kd = q.bfloat16().double(), k.bfloat16().double()
+    scale = (1.0 / np.sqrt(D)) * 1.4426950408889634
+    rows = slice(None) if tiny else slice(None, None, ROW_STRIDE)
+    out = []
+    for h in range(Hq):
+        s = torch.einsum('bnd,bmd->bnm', qd[:, h, rows], kd[:, h // (Hq // Hkv)]) * scale
+        s = s.masked_fill(~torch.from_numpy(mask[:, h // (Hq // Hkv), rows]), -float('inf'))
+        mx = s.max(-1, keepdim=True)[0]
+        out.append((mx.squeeze(-1) + torch.log2(torch.exp2(s - mx).sum(-1))).numpy())
+    return np.stack(out, 1)
+
+
 def run_case(name: str, case: dict, NAtSCache, Layer) -> dict:
     from oracle.nats_oracle import onehot_from_roles
     B, Hq, Hkv, N, D, C, SW = (case[x] for x in ('B', 'Hq', 'Hkv', 'N', 'D', 'C', 'SW'))
@@ -169,6 +208,7 @@ def run_case(name: str, case: dict, NAtSCache, Layer) -> dict:
         lc = cache.cache_model[0]
         tiny = D < 64
         out['prefill_out'] = o.numpy() if tiny else o[:, :, ::ROW_STRIDE].numpy()
+        out['prefill_M'] = log2_sum_exp2(q, k, mask, tiny)
         if tiny:
             out['prefill_mask'] = np.packbits(mask, axis=-1)
         else:
@@ -301,6 +341,86 @@ def run_token_case(name: str, case: dict) -> dict:
     return out
 
 
+def run_token_decode_case(name: str, case: dict) -> dict:
+    """Prefill, then single-token steps through the reference's ``NAtSLayerCache`` (update -> generate_mask(1) ->
+    attention -> post_update(1)).  After every step that triggers its batched update the sizes, the extent and the kept
+    K / V rows of every head are stored; the output of every step is stored too."""
+    from nats.components.cache.nats_layer_cache import NAtSLayerCache
+    from oracle.nats_oracle import onehot_from_roles, make_roles
+    B, Hq, Hkv, N, D, SW = (case[x] for x in ('B', 'Hq', 'Hkv', 'N', 'D', 'SW'))
+    roles = make_roles(B, Hkv, N, case['pg'], case['pl'], case['seed'], force_first_global=True)
+    q, k, v, steps = golden_inputs(case)
+    q, k, v = q.bfloat16().float(), k.bfloat16().float(), v.bfloat16().float()       # what a bf16 cache holds
+    lc = NAtSLayerCache(B, Hkv, SW, update_chunk_size=TOK_UPDATE, device=torch.device('cpu'))
+    n_rep = Hq // Hkv
+    out = {'roles': roles, 'in_checksum': checksum(*golden_inputs(case)[:3])}
+    with torch.no_grad():
+        keys, values = lc.update(k, v, onehot_from_roles(roles))
+        lc.generate_mask(N)
+        lc.post_update(N)
+        dec_out, upd_steps = [], []
+        for si, (q1, k1, v1, r1) in enumerate(steps):
+            q1, k1, v1 = q1.bfloat16().float(), k1.bfloat16().float(), v1.bfloat16().float()
+            keys, values = lc.update(k1, v1, onehot_from_roles(r1[..., None]))
+            mask = lc.generate_mask(1)
+            o1 = torch.nn.functional.scaled_dot_product_attention(
+                q1, keys.repeat_interleave(n_rep, 1), values.repeat_interleave(n_rep, 1), attn_mask=mask.repeat_interleave(n_rep, 1))
+            fill_before = lc.chunk_fill_size
+            lc.post_update(1)
+            dec_out.append(o1.numpy().copy())
+            if fill_before == TOK_UPDATE and lc.chunk_fill_size == 0:
+                j = len(upd_steps)
+                upd_steps.append(si)
+                sg, sl = lc.size_global_kv.numpy().copy(), lc.size_local_kv.numpy().copy()
+                n_ctx = int(lc.n_ctx_data)
+                out[f'u{j}_size_global'], out[f'u{j}_size_local'], out[f'u{j}_n_ctx_data'] = sg, sl, np.int64(n_ctx)
+                out[f'u{j}_cache_k'] = lc.cache_k[:, :, :n_ctx].numpy().copy()
+                out[f'u{j}_cache_v'] = lc.cache_v[:, :, :n_ctx].numpy().copy()
+                out[f'u{j}_valid'] = lc.valid_tokens[:, :, :n_ctx].numpy().copy()
+        out['update_steps'] = np.array(upd_steps)
+        out['dec_out'] = np.stack(dec_out)
+        out['dec_roles'] = np.stack([s[3] for s in steps])
+        out['dec_checksum'] = np.array([checksum(*s[:3]) for s in steps])
+    return out
+
+
+def role_inputs(case: dict):
+    """Hidden states [B, x_len, dim] of every call of a role-sampling case, regenerated from its seed."""
+    g = torch.Generator().manual_seed(case['seed'])
+    dim = case['Hq'] * case['D']
+    return [torch.randn(case['B'], n, dim, generator=g) for n in case['calls']]
+
+
+def run_role_case(name: str, case: dict, NAtSCache, Layer) -> dict:
+    """Drives the reference layer's own forward hooks call by call (prepare_x_values, whose
+    ``_sample_for_token_info_values_inference`` makes the roles; prepare_kv and multi_head_attention so that the cache's
+    fill state advances as in a real run) and stores the one-hot roles each call produced."""
+    B, Hq, Hkv, D, C, SW = (case[x] for x in ('B', 'Hq', 'Hkv', 'D', 'C', 'SW'))
+    torch.manual_seed(case['seed'])
+    layer = Layer(dim=Hq * D, n_heads=Hq, n_kv_heads=Hkv, layer_id=0, local_seq_max_length=SW, chunk_size=C,
+                  chunk_merge_method=case['method'])
+    layer.eval()
+    layer.global_token_enhanced_value = case['enh']
+    cache = NAtSCache(sliding_window_size=SW, chunk_size=C)
+    xs = role_inputs(case)
+    out = {'proj_weight': layer.proj_layer.weight.detach().numpy().copy(), 'in_checksum': checksum(*xs)}
+    pos = 0
+    with torch.no_grad():
+        for i, x in enumerate(xs):
+            x_len = x.shape[1]
+            out[f'c{i}_pre_fill'] = np.int64(cache.get_nats_chunk_fill_size(0))
+            out[f'c{i}_start_pos'] = np.int64(pos)
+            xq, xk, xv, info = layer.prepare_x_values(x, B, x_len, None, start_pos=pos, cache=cache)
+            tsi = info['token_states_info']
+            assert bool(((tsi == 0) | (tsi == 1)).all()) and bool((tsi.sum(-1) == 1).all())
+            out[f'c{i}_info'] = tsi.numpy().astype(np.uint8)           # one-hot [B, Hkv, chunks, 3]
+            keys, values = layer.prepare_kv(xq, xk, xv, pos, cache=cache, kwargs=info)
+            keys, values = layer.repeat_kv_values(keys, values)
+            layer.multi_head_attention(xq, keys, values, cache=cache, kwargs=info)
+            pos += x_len
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument('--reference', required=True)
@@ -309,11 +429,17 @@ def main():
     sys.path.insert(0, os.path.join(HERE, '..', '..'))
     NAtSCache, Layer = load_reference(args.reference)
     only = set(filter(None, args.only.split(',')))
-    for name, case in list(CASES.items()) + list(SEG_CASES.items()) + list(TOK_CASES.items()):
+    every = list(CASES.items()) + list(SEG_CASES.items()) + list(TOK_CASES.items()) + list(TOKDEC_CASES.items()) + \
+        list(ROLE_CASES.items())
+    for name, case in every:
         if only and name not in only:
             continue
         if name in TOK_CASES:
             res = run_token_case(name, case)
+        elif name in TOKDEC_CASES:
+            res = run_token_decode_case(name, case)
+        elif name in ROLE_CASES:
+            res = run_role_case(name, case, NAtSCache, Layer)
         else:
             res = (run_segmented_case if name in SEG_CASES else run_case)(name, case, NAtSCache, Layer)
         path = os.path.join(HERE, name + '.npz')

@@ -126,7 +126,7 @@ def test_prefill_role_extremes(special):
     assert_close_attn(o, orc.prefill_attention(q, k, v, roles, C, SW), special)
 
 
-@pytest.mark.parametrize('name', ['k64_mha', 'k128_gqa', 'k64_ragged', 'k128_decode'])
+@pytest.mark.parametrize('name', ['k64_mha', 'k128_gqa', 'k64_ragged', 'k128_decode', 'cfg1_mha_2048'])
 def test_prefill_matches_golden_fixture(name):
     """Against rows the reference's own eager path produced (fp32 inputs there, bf16-rounded here: the tolerance
     covers the input rounding too, which is why these cases use the bars of the spec and nothing tighter)."""
@@ -182,6 +182,24 @@ def test_forward_statistics_for_the_backward(B, Hq, Hkv, N, D, C, SW):
     assert np.array_equal(cnt.cpu().numpy(), cnt_ref)
     assert (lse.cpu() - lse_ref).abs().max().item() < 2e-2            # scores are bf16 products accumulated in fp32
     assert torch.equal(o, prefill_attention(qd, kd, vd, torch.from_numpy(roles).to(dev()), C, SW))
+
+
+@pytest.mark.parametrize('name', ['k64_mha', 'k128_gqa', 'k64_ragged', 'k128_decode', 'cfg1_mha_2048'])
+def test_forward_statistics_match_reference_mask_evaluation(name):
+    """M against the float64 evaluation of log2 sum exp2 over the reference's own mask (stored by the fixture script,
+    inputs rounded to bf16 there as here); visible-key counts against the same mask."""
+    from neuralattentionsearch_b200 import check_status
+    from neuralattentionsearch_b200.functional import nats_chunk_attention_fwd
+    case, fx, (q, k, v, _) = load(name)
+    qd, kd, vd = (t.to(dev()).bfloat16() for t in (q, k, v))
+    o, lse, cnt = nats_chunk_attention_fwd(qd, kd, vd, orc.onehot_from_roles(fx['roles']).to(dev()), None, True,
+                                           case['D'] ** -0.5, case['C'], n_rep=case['Hq'] // case['Hkv'],
+                                           local_seq_max_length=case['SW'])
+    check_status(dev())
+    got = lse[:, :, ::ROW_STRIDE].cpu().numpy()
+    assert np.abs(got - fx['prefill_M']).max() < 2e-2
+    ref_cnt = np.unpackbits(fx['prefill_mask_rows'], axis=-1)[..., :case['N']].sum(-1).repeat(case['Hq'] // case['Hkv'], axis=1)
+    assert np.array_equal(cnt[:, :, ::ROW_STRIDE].cpu().numpy(), ref_cnt)
 
 
 # ------------------------------------------------------------------------------------------------ eviction
@@ -447,6 +465,34 @@ def test_token_granular_prefill_matches_reference_cache(name):
     fx = dict(fx, pre_cache_k=ref_k, pre_cache_v=ref_v)
     check_token_granular_state(case, fx, lc.size_global_kv.cpu().numpy(), lc.size_local_kv.cpu().numpy(), lc.n_ctx_data,
                                lc.valid_tokens.cpu().numpy(), lc.cache_k.float().cpu().numpy(), lc.cache_v.float().cpu().numpy())
+
+
+@pytest.mark.parametrize('name', ['tokdec_tiny', 'tokdec_k64'])
+def test_token_granular_decode_state_at_reference_update_points(name):
+    """chunk_size 1, single tokens: right after each of the reference's batched updates (every 16 steps) the cache here
+    holds the reference's sizes, extent and kept rows bit for bit, and the step that follows gives the reference's output."""
+    from golden_util import load as load_any
+    from neuralattentionsearch_b200 import NAtSCache, check_status
+    from test_oracle_golden import check_token_granular_update
+    case, fx, (q, k, v, steps) = load_any(name)
+    B, Hq, Hkv, SW = case['B'], case['Hq'], case['Hkv'], case['SW']
+    cache = NAtSCache(SW, 1)
+    cache.update(k.to(dev()).bfloat16(), v.to(dev()).bfloat16(), 0,
+                 cache_kwargs={'token_states_info': orc.onehot_from_roles(fx['roles']).to(dev())})
+    cache.post_update(0, case['N'])
+    lc = cache.cache_model[0]
+    ups = fx['update_steps'].tolist()
+    for si, (q1, k1, v1, r1) in enumerate(steps):
+        info = orc.onehot_from_roles(r1[..., None]).to(dev())
+        cache.update(k1.to(dev()).bfloat16(), v1.to(dev()).bfloat16(), 0, cache_kwargs={'token_states_info': info, 'fused': True})
+        o = lc.decode_attention(q1.to(dev()).bfloat16())
+        cache.post_update(0, 1)
+        if si == 0 or si - 1 in ups:
+            assert (o.float().cpu() - torch.from_numpy(fx['dec_out'][si])).abs().max().item() <= 2e-2, f'step {si}'
+        if si in ups:
+            check_token_granular_update(case, fx, ups.index(si), lc.size_global_kv.cpu().numpy(), lc.size_local_kv.cpu().numpy(),
+                                        lc.n_ctx_data, lc.cache_k.float().cpu().numpy(), lc.cache_v.float().cpu().numpy())
+    check_status(dev())
 
 
 # ------------------------------------------------------------------------------------------------ module level

@@ -3,7 +3,7 @@ import numpy as np
 import pytest
 import torch
 
-from golden_util import CASES, ROW_STRIDE, SEG_CASES, TOK_CASES, load, segment_roles
+from golden_util import CASES, ROW_STRIDE, SEG_CASES, TOK_CASES, TOKDEC_CASES, load, segment_roles
 from oracle import nats_oracle as orc
 
 TINY = [n for n, c in CASES.items() if c['D'] < 64]
@@ -238,3 +238,56 @@ def test_token_granular_prefill_matches_reference(name):
     got = out.numpy() if tiny else out[:, :, ::ROW_STRIDE].numpy()
     np.testing.assert_allclose(got, fx['prefill_out'], rtol=1e-4, atol=2e-5)
     check_token_granular_state(case, fx, st.size_global, st.size_local, st.n_ctx_data, st.valid, st.cache_k, st.cache_v)
+
+
+@pytest.mark.parametrize('name', TINY + KERNEL)
+def test_log2_sum_exp2_matches_reference_mask_evaluation(name):
+    """M of the training forward: the oracle's statistic against the float64 evaluation over the reference's own mask
+    that the fixture stores (inputs rounded to bf16 on both sides)."""
+    case, fx, (q, k, v, _) = load(name)
+    bf = lambda t: t.bfloat16().float()
+    lse, cnt = orc.prefill_stats(bf(q), bf(k), fx['roles'], case['C'], case['SW'])
+    ref = fx['prefill_M']
+    got = lse.numpy() if case['D'] < 64 else lse[:, :, ::ROW_STRIDE].numpy()
+    np.testing.assert_allclose(got, ref, rtol=0, atol=1e-4)
+    key = 'prefill_mask' if 'prefill_mask' in fx else 'prefill_mask_rows'
+    ref_cnt = np.unpackbits(fx[key], axis=-1)[..., :case['N']].sum(-1).repeat(case['Hq'] // case['Hkv'], axis=1)
+    assert np.array_equal(cnt if case['D'] < 64 else cnt[:, :, ::ROW_STRIDE], ref_cnt)
+
+
+def check_token_granular_update(case, fx, j, size_global, size_local, n_ctx_data, cache_k, cache_v):
+    """Index-level state right after the reference's j-th batched update of single tokens: sizes, extent and the kept
+    K / V rows of every head (the ring is laid out differently, see check_token_granular_state)."""
+    SW = case['SW']
+    sg, sl = fx[f'u{j}_size_global'], fx[f'u{j}_size_local']
+    assert np.array_equal(size_global, sg) and np.array_equal(size_local, sl), f'update {j}'
+    assert n_ctx_data == int(fx[f'u{j}_n_ctx_data']), f'update {j}'
+    for b in range(case['B']):
+        for h in range(case['Hkv']):
+            n = sg[b, h] + sl[b, h]
+            assert np.array_equal(cache_k[b, h, SW:n], fx[f'u{j}_cache_k'][b, h, SW:n]), (j, b, h)
+            assert np.array_equal(cache_v[b, h, SW:n], fx[f'u{j}_cache_v'][b, h, SW:n]), (j, b, h)
+
+
+@pytest.mark.parametrize('name', list(TOKDEC_CASES))
+def test_token_granular_decode_state_at_reference_update_points(name):
+    """Single tokens through the token-granular cache.  The reference (NAtSLayerCache) places them in batches of 16; here
+    every token is placed at once.  Right after each of the reference's batched updates the two agree on sizes, extent and
+    kept rows, and the next step's output agrees too; in between the reference's outputs drift (tokens waiting for their
+    placement stay visible), which is not reproduced."""
+    case, fx, (q, k, v, steps) = load(name)
+    bf = lambda t: t.bfloat16().float()
+    st = orc.ChunkCacheOracle(case['B'], case['Hkv'], case['SW'], 1)
+    st.update(bf(k).numpy(), bf(v).numpy(), fx['roles'])
+    st.post_update(case['N'])
+    ups = fx['update_steps'].tolist()
+    assert len(ups) >= 3
+    for si, (q1, k1, v1, r1) in enumerate(steps):
+        st.update(bf(k1).numpy(), bf(v1).numpy(), r1[..., None])
+        o = orc.decode_attention(bf(q1), st.cache_k, st.cache_v, st.decode_mask())
+        st.post_update(1)
+        if si == 0 or si - 1 in ups:
+            np.testing.assert_allclose(o.numpy(), fx['dec_out'][si], rtol=1e-4, atol=2e-5, err_msg=f'step {si}')
+        if si in ups:
+            check_token_granular_update(case, fx, ups.index(si), st.size_global, st.size_local, st.n_ctx_data,
+                                        st.cache_k, st.cache_v)
