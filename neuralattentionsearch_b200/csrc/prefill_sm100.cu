@@ -2,21 +2,22 @@
 //
 // A work item = one 128-row query tile x one kv-head x up to two query heads of that kv-head's group.  The two heads
 // share every K/V tile that is loaded and keep the tensor pipe busy in turns: while the softmax warps of one head
-// work on S = Q.K^T in TMEM, the tensor core runs the other head's MMAs.  The kernel is persistent: one CTA per SM
-// takes items from a global counter (heaviest query tiles first).
+// work on its 128 x 128 score tile S = Q.K^T in TMEM, the tensor core runs the other head's O += P.V and next Q.K^T.
+// The kernel is persistent: one CTA per SM takes items from a global counter (heaviest query tiles first).
 //
-//   warp 0      TMA producer: Q of an item, then K and V of every kept KV tile through 2-stage rings
-//   warp 3      scheduler: fetches the next item and builds its kept-tile list while the current item runs
-//   warps 1,2   MMA issuers of head slot 0 / 1 (one elected lane each): S_h = Q_h.K^T (SS), O_h += P_h.V (TS, P from TMEM)
-//   warps 4-7   softmax of head slot 0: one thread per query row, S read with tcgen05.ld, online softmax in
-//   warps 8-11  softmax of head slot 1  registers, P written back over S as packed bf16 with tcgen05.st
+//   warp 0      TMA producer: K and V of every kept KV tile, item after item, through one ring of tile-sized slots
+//   warp 3      scheduler: fetches the next item, builds its kept-tile bitmap while the current item runs, loads its Q tiles
+//   warps 1,2   MMA issuers of head slot 0 / 1 (one elected lane each): S_h = Q_h.K^T (SS, N = 128), O_h += P_h.V (TS, P from TMEM)
+//   warps 4-7   softmax of head slot 0: one thread per query row, the 128-entry score row read with tcgen05.ld, online
+//   warps 8-11  softmax of head slot 1  softmax in registers, P written back over S as packed bf16 in two halves
 //
-// Which KV tiles are visited comes from the role bitmap: a list of kept tiles is built in shared memory from the
+// Which KV tiles are visited comes from the role bitmap: a bitmap of kept tiles is built in shared memory from the
 // per-tile max / min row limits (nats_b200_role_prep); tiles without a visible entry are never loaded.  Only tiles
 // whose min limit does not cover the whole query tile (and the diagonal) pay for per-element masking.
 //
-// TMEM (512 columns): S0 [0,128) S1 [128,256) O0 [256,256+D) O1 [384,384+D); P_h aliases the first 64 columns of S_h.
-// Every mbarrier wait is bounded: on a time-out the CTA raises the caller's status word, drains and exits.
+// TMEM (512 columns), head slot h: S_h [256 h, 256 h + 128), O_h [256 h + 128, 256 h + 128 + D); P_h (bf16) aliases
+// the first 64 columns of S_h.  Every mbarrier wait is bounded: on a time-out the CTA raises the caller's status
+// word, drains and exits.
 #include <cuda.h>
 
 #include "common.cuh"
@@ -33,14 +34,13 @@ constexpr int kPrefillThreads = 384;
 // setmaxnreg split: 128 * low + 256 * high must not exceed the 384 * 168 registers of the launch
 constexpr int kRegsLow = NATS_REGS_LOW, kRegsHigh = NATS_REGS_HIGH;
 static_assert(128 * kRegsLow + 256 * kRegsHigh <= 384 * 168, "setmaxnreg budget");
-#ifndef NATS_PINGPONG
-#define NATS_PINGPONG 1
+#ifndef NATS_F32X2
+#define NATS_F32X2 1
 #endif
-constexpr bool kPingPong = NATS_PINGPONG != 0;   // the two heads' warps that share a scheduler take turns on the MUFU pipe
-constexpr int kStages = 4;                              // K/V ring depth, in 64-row sub-tiles
-constexpr int kSub = 64;                                // key columns per sub-tile (two per kept 128-column tile)
-constexpr uint32_t kQBoxBytes = 128 * 64 * 2;           // one TMA box of Q: 128 rows x 64 bf16, 128-byte swizzled
-constexpr uint32_t kKvBoxBytes = kSub * 64 * 2;         // one TMA box of K or V: 64 rows x 64 bf16
+#ifndef NATS_MAX3
+#define NATS_MAX3 1
+#endif
+constexpr uint32_t kBoxBytes = 128 * 64 * 2;            // one TMA box: 128 rows x 64 bf16, 128-byte swizzled
 #ifndef NATS_RELAX_NS
 #define NATS_RELAX_NS 200
 #endif
@@ -50,9 +50,12 @@ constexpr int kRelaxNs = NATS_RELAX_NS;
 #endif
 constexpr int kRelaxProdNs = NATS_RELAX_PROD_NS;
 constexpr float kRescaleThreshold = 8.0f;               // log2 units: O is rescaled only when the row max grows by more
-constexpr unsigned long long kWaitLimitNs = 400ull * 1000ull * 1000ull;
+#ifndef NATS_WAIT_LIMIT_NS
+#define NATS_WAIT_LIMIT_NS (400ull * 1000ull * 1000ull)
+#endif
+constexpr unsigned long long kWaitLimitNs = NATS_WAIT_LIMIT_NS;
 
-enum : int { kErrQ = 1, kErrKFull, kErrVFull, kErrKEmpty, kErrVEmpty, kErrSFull, kErrPFull, kErrOFull, kErrTurn, kErrList, kErrOEmpty, kErrPvDone, kErrMufu };
+enum : int { kErrQ = 1, kErrKvFull, kErrKvEmpty, kErrSFull, kErrPFull, kErrOFull, kErrList, kErrOEmpty, kErrSmemAlign, kErrPipeLock };
 
 struct PrefillParams {
     __nv_bfloat16* o;                 // [B,Hq,N,D]
@@ -66,7 +69,7 @@ struct PrefillParams {
     // N query rows; query row i sits at position q_off + i of the KV sequence of Nkv rows (a first call has q_off = 0 and
     // Nkv = N; a call over an existing cache attends to the cache rows in front of its own tokens).
     // Nc / Ntk: chunks / 128-row tiles of the KV sequence, Nt: query tiles.
-    int Hq, Hkv, N, Nkv, q_off, C, Nc, Nt, Ntk, nrep, n_groups;   // n_groups = ceil(nrep / 2)
+    int Hq, Hkv, N, Nkv, q_off, C, Nc, Nt, Ntk, nrep, n_groups;   // n_groups = ceil(nrep / heads per item)
     float scale_log2;
 };
 
@@ -120,10 +123,22 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     }
 }
 
-__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2) {
+// L2 eviction priority of a TMA load: K / V tiles are read again by the CTAs that work on neighbouring query tiles and
+// should stay, Q tiles are read once
+__device__ __forceinline__ uint64_t l2_policy_evict_last() {
+    uint64_t pol;
+    asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(pol));
+    return pol;
+}
+__device__ __forceinline__ uint64_t l2_policy_evict_first() {
+    uint64_t pol;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+    return pol;
+}
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2, uint64_t policy) {
     asm volatile(
-        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
-        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1), "r"(c2) : "memory");
+        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%3, %4, %5}], [%2], %6;"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "l"(policy) : "memory");
 }
 __device__ __forceinline__ void prefetch_tmap(const CUtensorMap* map) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
@@ -160,6 +175,26 @@ __device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_
         "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
         ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+
+// The same with the descriptors given as (low word, shared high word): within one kernel only the start address and
+// the leading byte offset (low word) differ between operands, so the issuing thread adds small constants to 32-bit
+// registers instead of carrying 64-bit descriptors around.
+template <int ACC>
+__device__ __forceinline__ void mma_ss_lo(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t desc_hi, uint32_t idesc) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\tsetp.ne.b32 p, %5, 0;\n\t"
+        "mov.b64 da, {%1, %3};\n\tmov.b64 db, {%2, %3};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "n"(ACC) : "memory");
+}
+template <int ACC>
+__device__ __forceinline__ void mma_ts_lo(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t desc_hi, uint32_t idesc) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 db;\n\tsetp.ne.b32 p, %5, 0;\n\t"
+        "mov.b64 db, {%2, %3};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(desc_hi), "r"(idesc), "n"(ACC) : "memory");
 }
 
 // 32 lanes x 32 consecutive 32-bit columns: thread i of the warp gets its lane's columns
@@ -204,6 +239,12 @@ __device__ __forceinline__ uint32_t range_mask(int lo, int hi, int w) {
     return upto_b & ~((1u << a) - 1u);
 }
 
+// 32-byte store (one sector) to a 32-byte aligned global address
+__device__ __forceinline__ void st32(void* p, const uint32_t (&w)[8]) {
+    asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"
+                 ::"l"(p), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7]) : "memory");
+}
+
 __device__ __forceinline__ float ex2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -228,6 +269,73 @@ __host__ __device__ constexpr uint32_t instr_desc(int n, bool b_mn_major) {
     return (1u << 4) | (1u << 7) | (1u << 10) | ((b_mn_major ? 1u : 0u) << 16) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
 }
 
+// packed fp32 pairs: one instruction for two lanes of a multiply-add or add
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t d;
+    asm("fma.rn.ftz.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("add.rn.ftz.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+// 2^x for two values on the FMA and ALU pipes instead of the MUFU: round x to the nearest integer n with the
+// 1.5 * 2^23 trick, a cubic for 2^(x - n) on [-0.5, 0.5] (relative error 1.4e-4, far below the bf16 rounding of P), and n
+// added to the exponent field.  x is clamped at -126 (masked entries are -inf), which leaves about 1e-38 instead of 0.
+#ifndef NATS_POLY
+#define NATS_POLY 0
+#endif
+__device__ __forceinline__ void exp2_poly2(uint64_t x2, float& p0, float& p1) {
+    float x0, x1;
+    unpack2(x2, x0, x1);
+    const uint64_t xc = pack2(fmaxf(x0, -126.f), fmaxf(x1, -126.f));
+    const uint64_t magic = pack2(12582912.f, 12582912.f), neg_magic = pack2(-12582912.f, -12582912.f);
+    const uint64_t t2 = add2(xc, magic);
+    const uint64_t n2 = add2(t2, neg_magic);
+    const uint64_t f2 = fma2(n2, pack2(-1.f, -1.f), xc);
+    uint64_t q2 = fma2(f2, pack2(0.055029310f, 0.055029310f), pack2(0.24225681f, 0.24225681f));
+    q2 = fma2(q2, f2, pack2(0.69325304f, 0.69325304f));
+    q2 = fma2(q2, f2, pack2(0.99995136f, 0.99995136f));
+    float t0, t1, q0, q1;
+    unpack2(t2, t0, t1);
+    unpack2(q2, q0, q1);
+    p0 = __int_as_float(__float_as_int(q0) + (__float_as_int(t0) << 23));
+    p1 = __int_as_float(__float_as_int(q1) + (__float_as_int(t1) << 23));
+}
+
+__device__ __forceinline__ float max3(float a, float b, float c) {
+#if NATS_MAX3
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+#else
+    return fmaxf(fmaxf(a, b), c);
+#endif
+}
+
+#ifdef NATS_TRACE
+// development builds only: cycle stamps of one softmax warp and one issuer of CTA 0, summed per phase
+__device__ unsigned long long g_trace[64];
+#define TR_DECL(n) unsigned long long tr_acc[n] = {}; unsigned long long tr_t = clock64(); const bool tr_on = blockIdx.x == 0 && lane == 0
+#define TR_RESET() do { tr_t = clock64(); } while (0)
+#define TR(i) do { const unsigned long long t_ = clock64(); tr_acc[i] += t_ - tr_t; tr_t = t_; } while (0)
+#define TR_DUMP(base, n) do { if (tr_on) for (int i_ = 0; i_ < n; ++i_) g_trace[base + i_] = tr_acc[i_]; } while (0)
+#else
+#define TR_DECL(n)
+#define TR_RESET()
+#define TR(i)
+#define TR_DUMP(base, n)
+#endif
+
 // ---- shared memory --------------------------------------------------------------------------------
 struct ItemHeader {
     int valid;      // 0: no more work
@@ -235,75 +343,163 @@ struct ItemHeader {
     int b, bh;      // batch index, b * Hkv + kv-head
     int head0;      // query head of slot 0
     int nslots;     // 1 or 2 query heads in this item
-    int n_kept;     // kept 128-column KV tiles (each is processed as two 64-column sub-tiles)
+    int n_kept;     // kept 128-column KV tiles
     int pad;
 };
 
+constexpr int kBitWords = kMaxTiles / 32;
+
+// K/V ring: slots of one 128-row tile each, filled in the order K_0 V_0 K_1 V_1 ... of the kept tiles (all items in
+// one sequence).  A K slot is free again when both heads' Q.K^T of that tile have completed, a V slot after both P.V.
 template <int D>
-struct __align__(1024) PrefillSmem {
-    uint8_t q[2][128 * D * 2];             // one tile per head slot; D/64 boxes of 16 KB each
-    uint8_t kv[kStages][2][kSub * D * 2];  // per stage: K sub-tile, V sub-tile; D/64 boxes of 8 KB each
-    uint16_t list[2][kMaxTiles];           // kept KV tiles of an item, ascending; bit 15 = needs element masking (double buffered)
+struct PrefillSmem {
+    static constexpr int kHeads = D <= 128 ? 2 : 1;      // query heads of an item (head_dim 256: O fills the TMEM of one head pair)
+    static constexpr int kSlots = D == 256 ? 2 : D == 128 ? 5 : 8;
+    static constexpr uint32_t kTileBytes = 128 * D * 2;
+    uint8_t q[kHeads][kTileBytes];             // one Q tile per head slot; D/64 boxes of 16 KB each
+    uint8_t ring[kSlots][kTileBytes];          // K or V tile; D/64 boxes of 16 KB each
+    uint32_t keep[2][kBitWords];               // bit kt: KV tile kt of the item has a visible entry (double buffered)
+    uint32_t part[2][kBitWords];               // bit kt: the tile needs element masking
     ItemHeader item[2];
-    unsigned long long bar_q_full, bar_q_empty;
-    unsigned long long bar_kv_full[kStages], bar_kv_empty[kStages];
-    unsigned long long bar_s_full[2][2], bar_p_full[2][2], bar_pv_done[2], bar_o_full[2], bar_o_empty[2];
+    unsigned long long bar_q_full[2], bar_q_empty[2];          // per head slot: its Q tile has landed / its last Q.K^T of the item is done
+    unsigned long long bar_full[kSlots], bar_empty[kSlots];
+    unsigned long long bar_s_full[2], bar_p_full[2][2], bar_o_full[2], bar_o_empty[2];
     unsigned long long bar_list_full[2], bar_list_empty[2];
-    unsigned long long bar_mufu[2][4];     // [head slot][warp quarter]: permission to run the exponentials
     uint32_t tmem_base;
     int abort_flag;
+    int pipe_lock;                             // held by the issuer whose batch of MMAs is being queued
 };
+static_assert(sizeof(PrefillSmem<128>) <= 232448 && sizeof(PrefillSmem<256>) <= 232448, "shared memory of the widest kernels");
 
 constexpr int kListConsumers = 1 + 2 + 8;     // producer, two issuers, one lane of each of the eight softmax warps
 
+// Walks the set bits of an item's kept-tile bitmap in ascending order.
+struct TileWalk {
+    const uint32_t* keep;
+    const uint32_t* part;
+    int w;
+    uint32_t cur, pcur;
+    __device__ __forceinline__ void init(const uint32_t* k, const uint32_t* p) {
+        keep = k; part = p; w = 0; cur = k[0]; pcur = p[0];
+    }
+    // next kept tile; the caller asks for no more tiles than the item has
+    __device__ __forceinline__ int next(bool& partial) {
+        while (cur == 0u) { ++w; cur = keep[w]; pcur = part[w]; }
+        const int b = __ffs(cur) - 1;
+        cur &= cur - 1u;
+        partial = (pcur >> b) & 1u;
+        return w * 32 + b;
+    }
+};
+
+// A bounded wait whose outcome is the same for every lane of the warp (all 32 lanes call it): lanes may see a time-out
+// or the CTA's abort flag at different polls, and what follows (.sync.aligned instructions, __syncwarp) needs the
+// whole warp on one path.
+template <int RELAX = 0>
+__device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int32_t* status, int code) {
+    const bool ok = mbar_wait<RELAX>(bar, parity, abort_flag, status, code);
+    return __all_sync(0xffffffffu, ok);
+}
+
+// The two issuers queue their MMAs in whole batches (the P.V of a tile and the Q.K^T of the next): the tensor pipe runs
+// MMAs in the order they were queued, so batches that interleaved would finish together and keep the two heads in step --
+// both in their softmax, then both waiting for the tensor pipe.  With whole batches one head's scores are ready a batch
+// earlier than the other's, and from then on one head's softmax overlaps the other head's MMAs.
+#ifndef NATS_PIPE_LOCK
+#define NATS_PIPE_LOCK 1
+#endif
+#ifndef NATS_PV_EARLY
+#define NATS_PV_EARLY 0
+#endif
+__device__ __forceinline__ bool pipe_acquire(int* lock, int lane, volatile int* abort_flag, int32_t* status) {
+#if NATS_PIPE_LOCK
+    int got = 1;
+    if (lane == 0) {
+        if (atomicCAS(lock, 0, 1) != 0) {
+            const unsigned long long t0 = global_ns();
+            got = 0;
+#pragma unroll 1
+            for (uint32_t it = 0;; ++it) {
+                __nanosleep(40);
+                if (atomicCAS(lock, 0, 1) == 0) { got = 1; break; }
+                if ((it & 63u) == 63u) {
+                    if (*abort_flag) break;
+                    if (global_ns() - t0 > kWaitLimitNs) {
+                        *abort_flag = 1;
+                        atomicCAS(status, 0, kErrPipeLock);
+                        break;
+                    }
+                }
+            }
+        }
+    }
+    return __shfl_sync(0xffffffffu, got, 0) != 0;
+#else
+    return true;
+#endif
+}
+__device__ __forceinline__ void pipe_release(int* lock, int lane) {
+#if NATS_PIPE_LOCK
+    __syncwarp();
+    if (lane == 0) atomicExch(lock, 0);
+#endif
+}
+
 // Persistent kernel: every CTA takes work items (query tile x kv-head x head pair) from a global counter until none is
-// left.  Per-item set-up (kept-tile list, Q load) and tear-down (O -> global) overlap the main loops of the neighbouring
-// items: warp 3 prepares the list of the next item while the current one runs, the producer streams the next item's K/V
-// through the same ring without a bubble, Q of the next item is loaded as soon as the last Q.K^T of the current one
-// has completed, and a head's epilogue only delays that head's own chain.
+// left.  Per-item set-up (kept-tile bitmap, Q load) and tear-down (O -> global) overlap the main loops of the
+// neighbouring items: warp 3 prepares the bitmap of the next item while the current one runs, the producer streams the
+// next item's K/V through the same ring without a bubble, Q of the next item is loaded as soon as the last Q.K^T of the
+// current one has completed, and a head's epilogue only delays that head's own chain.
 //
-// A kept 128-column KV tile is processed as two 64-column sub-tiles, and every head has TWO score buffers in TMEM
-// (S_a, S_b: 64 columns each) next to its 128-column O accumulator.  S = Q.K^T of sub-tile u+1 is therefore computed
-// while the softmax warps still work on sub-tile u: the softmax of a head runs back to back and only O += P.V waits for
-// it, so the tensor pipe is kept busy by two independent chains instead of being stalled by one softmax latency per tile.
+// Per head and kept tile j the chain is  S = Q.K_j^T (8 or 4 MMAs of N = 128)  ->  softmax over the 128-entry row held in
+// registers  ->  P (bf16) over the first 64 columns of S, published in two halves of 64 keys  ->  O += P.V_j (the MMAs of
+// the first 64 keys are issued while the second half of P is still being computed)  ->  S = Q.K_{j+1}^T.  The two heads
+// run this chain half a period apart, so that one head's softmax (MUFU and issue slots of the four SM sub-partitions)
+// overlaps the other head's MMAs on the tensor pipe.
 template <int D>
 __global__ void __launch_bounds__(kPrefillThreads, 1)
 prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                const __grid_constant__ CUtensorMap map_v, const PrefillParams p) {
-    extern __shared__ uint8_t smem_raw[];
-    PrefillSmem<D>& sm = *reinterpret_cast<PrefillSmem<D>*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    using Smem = PrefillSmem<D>;
+    Smem& sm = *reinterpret_cast<Smem*>(smem_raw);
     constexpr int NBOX = D / 64;                       // TMA boxes per tile
-    constexpr uint32_t Q_BYTES = NBOX * kQBoxBytes;    // one Q tile (128 rows)
-    constexpr uint32_t SUB_BYTES = NBOX * kKvBoxBytes; // one K or V sub-tile (64 rows)
-    constexpr uint32_t IDESC_QK = instr_desc(kSub, false);
+    constexpr int NS = Smem::kSlots;
+    constexpr uint32_t TILE_BYTES = Smem::kTileBytes;  // one Q, K or V tile (128 rows)
+    constexpr uint32_t IDESC_QK = instr_desc(kTile, false);
     constexpr uint32_t IDESC_PV = instr_desc(D, true);
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     volatile int* abort_flag = &sm.abort_flag;
 
-    if (tid == 0) sm.abort_flag = (*reinterpret_cast<volatile int32_t*>(p.status) != 0);
+    if (tid == 0) {
+        int bad = (*reinterpret_cast<volatile int32_t*>(p.status) != 0);
+        if ((smem_u32(smem_raw) & 1023u) != 0u) {      // the swizzled tiles need a 1024-byte aligned base
+            atomicCAS(p.status, 0, kErrSmemAlign);
+            bad = 1;
+        }
+        sm.abort_flag = bad;
+        sm.pipe_lock = 0;
+    }
     __syncthreads();
     if (sm.abort_flag) return;                         // an earlier CTA gave up: do not start (uniform for the CTA)
 
     // ---- set-up: barriers, TMEM ----
     if (tid == 0) {
-        mbar_init(smem_u32(&sm.bar_q_full), 1);
-        mbar_init(smem_u32(&sm.bar_q_empty), 2);                   // one commit per MMA issuer
-        for (int s = 0; s < kStages; ++s) {
-            mbar_init(smem_u32(&sm.bar_kv_full[s]), 1);
-            mbar_init(smem_u32(&sm.bar_kv_empty[s]), 2);
+        for (int s = 0; s < NS; ++s) {
+            mbar_init(smem_u32(&sm.bar_full[s]), 1);
+            mbar_init(smem_u32(&sm.bar_empty[s]), 2);
         }
         for (int h = 0; h < 2; ++h) {
-            for (int x = 0; x < 2; ++x) {
-                mbar_init(smem_u32(&sm.bar_s_full[h][x]), 1);
-                mbar_init(smem_u32(&sm.bar_p_full[h][x]), 4);              // one arrival per softmax warp
-            }
-            mbar_init(smem_u32(&sm.bar_pv_done[h]), 1);
+            mbar_init(smem_u32(&sm.bar_q_full[h]), 1);
+            mbar_init(smem_u32(&sm.bar_q_empty[h]), 1);              // one arrival per item and head slot
+            mbar_init(smem_u32(&sm.bar_s_full[h]), 1);
+            mbar_init(smem_u32(&sm.bar_p_full[h][0]), 4);          // one arrival per softmax warp
+            mbar_init(smem_u32(&sm.bar_p_full[h][1]), 4);
             mbar_init(smem_u32(&sm.bar_o_full[h]), 1);
             mbar_init(smem_u32(&sm.bar_o_empty[h]), 4);
             mbar_init(smem_u32(&sm.bar_list_full[h]), 1);
             mbar_init(smem_u32(&sm.bar_list_empty[h]), kListConsumers);
-            for (int x = 0; x < 4; ++x) mbar_init(smem_u32(&sm.bar_mufu[h][x]), 1);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         prefetch_tmap(&map_q);
@@ -324,12 +520,14 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     if (warp < 4) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsLow));      // one site for the whole warpgroup
 
     if (warp == 3) {
-        // =============================== scheduler: next work item and its kept-tile list ===============================
+        // =============================== scheduler: next work item and its kept-tile bitmap ===============================
         const int per_z = p.Nt * p.Hkv * p.n_groups;
         bool ok = true;
+        int q_loads[2] = {0, 0};
+        const uint64_t pol_q = l2_policy_evict_first();
         for (int ic = 0; ok; ++ic) {
             const int slot = ic & 1, use = ic >> 1;
-            if (use > 0) ok = mbar_wait<kRelaxNs>(smem_u32(&sm.bar_list_empty[slot]), (use - 1) & 1, abort_flag, p.status, kErrList);
+            if (use > 0) ok = warp_wait<kRelaxNs>(smem_u32(&sm.bar_list_empty[slot]), (use - 1) & 1, abort_flag, p.status, kErrList);
             if (!ok) break;
             int w = 0;
             if (lane == 0) w = atomicAdd(p.work_counter, 1);
@@ -347,21 +545,23 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                 const int kt_last = q_hi / kTile;
                 const int32_t* tmax = p.tile_max + (size_t)bh * p.Ntk;
                 const int32_t* tmin = p.tile_min + (size_t)bh * p.Ntk;
-                for (int s0 = 0; s0 <= kt_last; s0 += 32) {        // ordered compaction of the tiles 0..kt_last with a visible entry
+                for (int s0 = 0; s0 <= kt_last; s0 += 32) {        // tiles 0..kt_last with a visible entry
                     const int kt = s0 + lane;
                     const bool keep = kt <= kt_last && tmax[kt] >= q_lo;
+                    // element masking is needed where the causal edge or a chunk's row limit cuts through the tile
+                    const bool partial = keep && (kt * kTile + kTile - 1 > q_lo || tmin[kt] < q_hi);
                     const unsigned m = __ballot_sync(0xffffffffu, keep);
-                    if (keep) {
-                        // element masking is needed where the causal edge or a chunk's row limit cuts through the tile
-                        const bool partial = kt * kTile + kTile - 1 > q_lo || tmin[kt] < q_hi;
-                        sm.list[slot][n_kept + __popc(m & ((1u << lane) - 1u))] = (uint16_t)(kt | (partial ? 0x8000 : 0));
+                    const unsigned pm = __ballot_sync(0xffffffffu, partial);
+                    if (lane == 0) {
+                        sm.keep[slot][s0 >> 5] = m;
+                        sm.part[slot][s0 >> 5] = pm;
                     }
                     n_kept += __popc(m);
                 }
                 if (lane == 0) {
                     ItemHeader hd;
-                    hd.valid = 1; hd.t = t; hd.b = z; hd.bh = bh; hd.head0 = hkv * p.nrep + grp * 2;
-                    hd.nslots = min(2, p.nrep - grp * 2); hd.n_kept = n_kept; hd.pad = 0;
+                    hd.valid = 1; hd.t = t; hd.b = z; hd.bh = bh; hd.head0 = hkv * p.nrep + grp * Smem::kHeads;
+                    hd.nslots = min(Smem::kHeads, p.nrep - grp * Smem::kHeads); hd.n_kept = n_kept; hd.pad = 0;
                     sm.item[slot] = hd;
                 }
             } else if (lane == 0) {
@@ -370,148 +570,215 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&sm.bar_list_full[slot]));
             if (!have) break;
+            // Q of this item, head slot by head slot: a slot is reloaded as soon as that head's last Q.K^T of the previous
+            // item has completed (the K/V producer is not held up by it, and one head does not wait for the other)
+            const ItemHeader hd = sm.item[slot];
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                if (!ok) break;
+                if (ic > 0) ok = warp_wait<kRelaxNs>(smem_u32(&sm.bar_q_empty[h]), (ic - 1) & 1, abort_flag, p.status, kErrQ);
+                if (!ok) break;
+                if (h < hd.nslots) {
+                    if (lane == 0) {
+                        mbar_expect_tx(smem_u32(&sm.bar_q_full[h]), TILE_BYTES);
+                        for (int x = 0; x < NBOX; ++x)
+                            tma_load_3d(smem_u32(&sm.q[h][x * kBoxBytes]), &map_q, smem_u32(&sm.bar_q_full[h]), x * 64, hd.t * kTile,
+                                        hd.b * p.Hq + hd.head0 + h, pol_q);
+                    }
+                    ++q_loads[h];
+                }
+                __syncwarp();
+            }
+        }
+        if (!ok) {
+            // given up: let Q copies that are still in flight land before the shared memory is released
+#pragma unroll
+            for (int h = 0; h < 2; ++h)
+                if (q_loads[h] > 0) mbar_wait(smem_u32(&sm.bar_q_full[h]), (q_loads[h] - 1) & 1, nullptr, p.status, kErrQ);
         }
     } else if (warp == 0) {
         // =============================== TMA producer ===============================
-        uint32_t g = 0;                                 // sub-tiles pushed through the K/V ring so far (all items)
+        uint32_t g = 0;                                 // ring slots filled so far (all items): two per kept tile
+        const uint64_t pol_kv = l2_policy_evict_last();
         bool ok = true;
         for (int ic = 0; ok; ++ic) {
             const int slot = ic & 1;
-            ok = mbar_wait(smem_u32(&sm.bar_list_full[slot]), (ic >> 1) & 1, abort_flag, p.status, kErrList);
+            ok = warp_wait(smem_u32(&sm.bar_list_full[slot]), (ic >> 1) & 1, abort_flag, p.status, kErrList);
             if (!ok) break;
             const ItemHeader hd = sm.item[slot];
             if (!hd.valid) break;
-            // Q of this item may overwrite the previous one once both issuers have committed their last Q.K^T
-            if (ic > 0) ok = mbar_wait(smem_u32(&sm.bar_q_empty), (ic - 1) & 1, abort_flag, p.status, kErrQ);
-            if (!ok) break;
-            if (lane == 0) {
-                mbar_expect_tx(smem_u32(&sm.bar_q_full), hd.nslots * Q_BYTES);
-                for (int h = 0; h < hd.nslots; ++h)
-                    for (int x = 0; x < NBOX; ++x)
-                        tma_load_3d(smem_u32(&sm.q[h][x * kQBoxBytes]), &map_q, smem_u32(&sm.bar_q_full), x * 64, hd.t * kTile,
-                                    hd.b * p.Hq + hd.head0 + h);
-            }
-            for (int u = 0; u < 2 * hd.n_kept && ok; ++u, ++g) {
-                const int kt = sm.list[slot][u >> 1] & 0x7fff;
-                const int row0 = kt * kTile + (u & 1) * kSub;
-                const int s = g % kStages;
-                const uint32_t ph = (g / kStages) & 1;
-                if (g >= kStages) ok = mbar_wait<kRelaxProdNs>(smem_u32(&sm.bar_kv_empty[s]), ph ^ 1, abort_flag, p.status, kErrKEmpty);
-                if (!ok) break;
-                if (lane == 0) {
-                    mbar_expect_tx(smem_u32(&sm.bar_kv_full[s]), 2 * SUB_BYTES);
-                    for (int x = 0; x < NBOX; ++x)
-                        tma_load_3d(smem_u32(&sm.kv[s][0][x * kKvBoxBytes]), &map_k, smem_u32(&sm.bar_kv_full[s]), x * 64, row0, hd.bh);
-                    for (int x = 0; x < NBOX; ++x)
-                        tma_load_3d(smem_u32(&sm.kv[s][1][x * kKvBoxBytes]), &map_v, smem_u32(&sm.bar_kv_full[s]), x * 64, row0, hd.bh);
+            TileWalk walk;
+            walk.init(sm.keep[slot], sm.part[slot]);
+            for (int j = 0; j < hd.n_kept && ok; ++j) {
+                bool partial;
+                const int row0 = walk.next(partial) * kTile;
+#pragma unroll 1
+                for (int kv = 0; kv < 2 && ok; ++kv, ++g) {
+                    const int s = g % NS;
+                    if (g >= (uint32_t)NS) ok = warp_wait<kRelaxProdNs>(smem_u32(&sm.bar_empty[s]), ((g / NS) & 1) ^ 1, abort_flag, p.status, kErrKvEmpty);
+                    if (!ok) break;
+                    if (lane == 0) {
+                        mbar_expect_tx(smem_u32(&sm.bar_full[s]), TILE_BYTES);
+                        const CUtensorMap* map = kv == 0 ? &map_k : &map_v;
+                        for (int x = 0; x < NBOX; ++x)
+                            tma_load_3d(smem_u32(&sm.ring[s][x * kBoxBytes]), map, smem_u32(&sm.bar_full[s]), x * 64, row0, hd.bh, pol_kv);
+                    }
+                    __syncwarp();
                 }
-                __syncwarp();
             }
             if (ok && lane == 0) mbar_arrive(smem_u32(&sm.bar_list_empty[slot]));
         }
         if (!ok) {
             // given up: let copies that are still in flight land before the shared memory is released
-            for (uint32_t x = g > kStages ? g - kStages : 0; x < g; ++x)
-                mbar_wait(smem_u32(&sm.bar_kv_full[x % kStages]), (x / kStages) & 1, nullptr, p.status, kErrKFull);
+            for (uint32_t x = g > (uint32_t)NS ? g - NS : 0; x < g; ++x)
+                mbar_wait(smem_u32(&sm.bar_full[x % NS]), (x / NS) & 1, nullptr, p.status, kErrKvFull);
         }
     } else if (warp == 1 || warp == 2) {
         // =============================== MMA issuers: warp 1 for head slot 0, warp 2 for head slot 1 ===============================
-        // Per head and 64-column sub-tile u:  S[u & 1] = Q_h.K_u^T  (issued two sub-tiles ahead of the softmax) and
-        // O_h += P_u.V_u once the softmax warps have written P_u over S[u & 1].  S[u & 1] is overwritten by sub-tile u + 2
-        // only after the MMA that reads P_u has been issued (same thread, so the tensor pipe keeps the order).
-        // A K/V stage is released when both issuers have committed its P.V; an issuer whose head slot is empty in an item
-        // (odd group size) only keeps the barrier counts going.
+        // Per head and kept tile j:  O_h += P_j.V_j in two halves (as the halves of P arrive), then S_h = Q_h.K_{j+1}^T,
+        // which overwrites P_j: the tensor pipe runs one thread's MMAs in issue order.  A ring slot is released when both
+        // issuers have committed the MMAs that read it; an issuer whose head slot is empty in an item (odd group size)
+        // only keeps the barrier counts going.
         const int h = warp - 1;
-        constexpr uint32_t Q16 = Q_BYTES >> 4, SUB16 = SUB_BYTES >> 4, STAGE16 = (2 * SUB_BYTES) >> 4;
-        const uint64_t q_desc = smem_desc(smem_u32(&sm.q[0][0]), 16, 1024) + (uint64_t)(h * Q16);
-        const uint64_t k_desc0 = smem_desc(smem_u32(&sm.kv[0][0][0]), 16, 1024);
-        const uint64_t v_desc0 = smem_desc(smem_u32(&sm.kv[0][1][0]), kKvBoxBytes, 1024);
+        constexpr uint32_t T16 = TILE_BYTES >> 4;
+        // descriptors as (low word, high word): the high word (stride byte offset 1024, version, 128-byte swizzle) is the
+        // same for Q, K and V; the low word holds the start address >> 4 and the leading byte offset >> 4
+        const uint64_t q_desc = smem_desc(smem_u32(&sm.q[0][0]), 16, 1024) + (uint64_t)(h < Smem::kHeads ? h * T16 : 0);
+        const uint64_t k_desc0 = smem_desc(smem_u32(&sm.ring[0][0]), 16, 1024);
+        const uint64_t v_desc0 = smem_desc(smem_u32(&sm.ring[0][0]), kBoxBytes, 1024);
+        const uint32_t desc_hi = (uint32_t)(q_desc >> 32);
+        const uint32_t q_lo = (uint32_t)q_desc, k_lo0 = (uint32_t)k_desc0, v_lo0 = (uint32_t)v_desc0;
         const uint32_t tS = tmem + h * 256, tO = tmem + h * 256 + 128;
-        auto issue_qk = [&](int s, int buf) {
-            // S[buf][128 x 64] = Q_h[128 x D] . K_u[64 x D]^T : D/16 MMAs of K = 16
-            const uint64_t kd = k_desc0 + (uint64_t)(s * STAGE16);
-            const uint32_t dS = tS + buf * kSub;
-            mma_ss<0>(dS, q_desc, kd, IDESC_QK);
+        auto issue_qk = [&](int s) {
+            // S[128 x 128] = Q_h[128 x D] . K_j[128 x D]^T : D/16 MMAs of K = 16
+            const uint32_t kl = k_lo0 + (uint32_t)s * T16;
+            mma_ss_lo<0>(tS, q_lo, kl, desc_hi, IDESC_QK);
 #pragma unroll
             for (int ks = 1; ks < D / 16; ++ks) {
-                const uint32_t qoff = ((ks / 4) * kQBoxBytes + (ks % 4) * 32) >> 4;
-                const uint32_t koff = ((ks / 4) * kKvBoxBytes + (ks % 4) * 32) >> 4;
-                mma_ss<1>(dS, q_desc + qoff, kd + koff, IDESC_QK);
+                const uint32_t off = ((ks / 4) * kBoxBytes + (ks % 4) * 32) >> 4;
+                mma_ss_lo<1>(tS, q_lo + off, kl + off, desc_hi, IDESC_QK);
             }
         };
-        auto issue_pv = [&](int s, int buf, bool first) {
-            // O_h[128 x D] (+)= P_u[128 x 64] . V_u[64 x D] : 4 MMAs of K = 16; V is MN-major (D contiguous)
-            const uint64_t vd = v_desc0 + (uint64_t)(s * STAGE16);
-            const uint32_t aP = tS + buf * kSub;
-            mma_ts(tO, aP, vd, IDESC_PV, first ? 0u : 1u);
+        auto issue_pv_half = [&](int s, int half, bool first) {
+            // O_h[128 x D] (+)= P_j[128 x 64 keys of this half] . V_j[64 x D] : 4 MMAs of K = 16; V is MN-major (D contiguous)
+            const uint32_t vl = v_lo0 + (uint32_t)s * T16 + (uint32_t)(half * 4 * (2048 >> 4));
+            const uint32_t aP = tS + half * 32;
+            if (first) mma_ts_lo<0>(tO, aP, vl, desc_hi, IDESC_PV);
+            else mma_ts_lo<1>(tO, aP, vl, desc_hi, IDESC_PV);
 #pragma unroll
-            for (int ks = 1; ks < kSub / 16; ++ks) mma_ts(tO, aP + ks * 8, vd + (uint64_t)(ks * (2048 >> 4)), IDESC_PV, 1u);
+            for (int k4 = 1; k4 < 4; ++k4) mma_ts_lo<1>(tO, aP + k4 * 8, vl + (uint32_t)(k4 * (2048 >> 4)), desc_hi, IDESC_PV);
         };
-        (void)SUB16;
-        uint32_t g = 0;          // sub-tiles through the K/V ring (all items, both issuers count alike)
-        uint32_t gu = 0;         // sub-tiles of this head (items in which its slot is used); even at every item start
+        TR_DECL(8);
+#ifdef NATS_TRACE
+        unsigned long long tr_lock = 0, tr_pv = 0;
+#endif
+        uint32_t g = 0;          // ring slots consumed so far (all items, both issuers count alike)
+        uint32_t gt = 0;         // tiles of this head (items in which its slot is used)
         uint32_t na = 0;         // items in which this head's slot was used
         bool ok = true;
         for (int ic = 0; ok; ++ic) {
             const int slot = ic & 1;
-            ok = mbar_wait(smem_u32(&sm.bar_list_full[slot]), (ic >> 1) & 1, abort_flag, p.status, kErrList);
+            ok = warp_wait(smem_u32(&sm.bar_list_full[slot]), (ic >> 1) & 1, abort_flag, p.status, kErrList);
             if (!ok) break;
             const ItemHeader hd = sm.item[slot];
             if (!hd.valid) break;
-            const int n2 = 2 * hd.n_kept;
+            const int n = hd.n_kept;
             const bool active = h < hd.nslots;
-            if (active) ok = mbar_wait(smem_u32(&sm.bar_q_full), ic & 1, abort_flag, p.status, kErrQ);
-            // ---- the first two score buffers ----
-            for (int x = 0; x < 2 && ok; ++x) {
-                const uint32_t gx = g + x;
-                ok = mbar_wait(smem_u32(&sm.bar_kv_full[gx % kStages]), (gx / kStages) & 1, abort_flag, p.status, kErrKFull);
-                if (!ok) break;
-                tc_fence_after();
-                if (lane == 0) {
-                    if (active) {
-                        issue_qk(gx % kStages, x);
-                        tc_commit(smem_u32(&sm.bar_s_full[h][x]));
-                    }
-                    if (x == 1 && n2 == 2) tc_commit(smem_u32(&sm.bar_q_empty));
-                }
-                __syncwarp();
-            }
-            // ---- sub-tiles ----
-            for (int u = 0; u < n2 && ok; ++u) {
-                const uint32_t gs = g + u;
-                const int s = gs % kStages, buf = u & 1;
-                const bool more = u + 2 < n2;
+            if (active) ok = warp_wait(smem_u32(&sm.bar_q_full[h]), na & 1, abort_flag, p.status, kErrQ);
+            // ---- S of the first tile ----
+            if (ok) ok = warp_wait(smem_u32(&sm.bar_full[g % NS]), (g / NS) & 1, abort_flag, p.status, kErrKvFull);
+            if (ok && active) ok = pipe_acquire(&sm.pipe_lock, lane, abort_flag, p.status);
+            if (!ok) break;
+            tc_fence_after();
+            if (lane == 0) {
                 if (active) {
-                    ok = mbar_wait(smem_u32(&sm.bar_p_full[h][buf]), ((gu + u) >> 1) & 1, abort_flag, p.status, kErrPFull);
-                    // the first P.V of an item overwrites O_h: the previous item's epilogue must have read it
-                    if (ok && u == 0 && na > 0) ok = mbar_wait(smem_u32(&sm.bar_o_empty[h]), (na - 1) & 1, abort_flag, p.status, kErrOEmpty);
+                    issue_qk(g % NS);
+                    tc_commit(smem_u32(&sm.bar_s_full[h]));
                 } else {
-                    ok = mbar_wait(smem_u32(&sm.bar_kv_full[s]), (gs / kStages) & 1, abort_flag, p.status, kErrKFull);
+                    // an empty head slot only keeps the counts going; for a used one the head's softmax warps release the
+                    // ring slots and the Q tile when they see the scores (a commit costs the issuer ~50 cycles each)
+                    mbar_arrive(smem_u32(&sm.bar_empty[g % NS]));
+                    if (n == 1) mbar_arrive(smem_u32(&sm.bar_q_empty[h]));
                 }
-                if (ok && more) ok = mbar_wait(smem_u32(&sm.bar_kv_full[(gs + 2) % kStages]), ((gs + 2) / kStages) & 1, abort_flag, p.status, kErrKFull);
+            }
+            if (active) pipe_release(&sm.pipe_lock, lane);
+            __syncwarp();
+            // ---- tiles ----
+            for (int j = 0; j < n && ok; ++j) {
+                const uint32_t gv = g + 2 * j + 1;             // ring index of V_j; K_{j+1} follows it
+                const int sv = gv % NS;
+                TR(0);
+                ok = warp_wait(smem_u32(&sm.bar_full[sv]), (gv / NS) & 1, abort_flag, p.status, kErrKvFull);
+                TR(1);
+                const bool more = j + 1 < n;
+                const uint32_t gk = gv + 1;
+                if (ok && active) {
+                    ok = warp_wait(smem_u32(&sm.bar_p_full[h][0]), (gt + j) & 1, abort_flag, p.status, kErrPFull);
+                    TR(2);
+                    // the first P.V of an item overwrites O_h: the previous item's epilogue must have read it
+                    if (ok && j == 0 && na > 0) ok = warp_wait(smem_u32(&sm.bar_o_empty[h]), (na - 1) & 1, abort_flag, p.status, kErrOEmpty);
+#if NATS_PV_EARLY
+                    // the first half of P.V goes to the tensor pipe while the second half of P is still being computed
+                    if (!ok) break;
+                    tc_fence_after();
+                    if (lane == 0) issue_pv_half(sv, 0, j == 0);
+                    __syncwarp();
+#endif
+                    TR(3);
+                    if (ok) ok = warp_wait(smem_u32(&sm.bar_p_full[h][1]), (gt + j) & 1, abort_flag, p.status, kErrPFull);
+                    TR(4);
+                }
+                if (ok && more) ok = warp_wait(smem_u32(&sm.bar_full[gk % NS]), (gk / NS) & 1, abort_flag, p.status, kErrKvFull);
+                TR(5);
+                // everything the batch needs is there: queue it as a whole.  (The lock is never held across a wait for a
+                // ring slot: the slot may be one the other head still has to release, which it can only do by queueing its
+                // own batch.)
+                if (ok && active) ok = pipe_acquire(&sm.pipe_lock, lane, abort_flag, p.status);
                 if (!ok) break;
+#ifdef NATS_TRACE
+                { const unsigned long long t_ = clock64(); tr_lock += t_ - tr_t; tr_t = t_; }
+#endif
                 tc_fence_after();
                 if (lane == 0) {
                     if (active) {
-                        issue_pv(s, buf, u == 0);
-                        tc_commit(smem_u32(&sm.bar_pv_done[h]));
-                        if (u == n2 - 1) tc_commit(smem_u32(&sm.bar_o_full[h]));
+#if !NATS_PV_EARLY
+                        issue_pv_half(sv, 0, j == 0);
+#endif
+                        issue_pv_half(sv, 1, false);
+                        if (!more) tc_commit(smem_u32(&sm.bar_o_full[h]));
+                        tc_commit(smem_u32(&sm.bar_empty[sv]));        // V_j is free as soon as P.V has run: the ring is short
+                    } else {
+                        mbar_arrive(smem_u32(&sm.bar_empty[sv]));
                     }
-                    tc_commit(smem_u32(&sm.bar_kv_empty[s]));
+#ifdef NATS_TRACE
+                    { const unsigned long long t_ = clock64(); tr_pv += t_ - tr_t; tr_t = t_; }
+#endif
+                }
+                if (lane == 0) {
                     if (more) {
                         if (active) {
-                            issue_qk((gs + 2) % kStages, buf);
-                            tc_commit(smem_u32(&sm.bar_s_full[h][buf]));
+                            issue_qk(gk % NS);
+                            tc_commit(smem_u32(&sm.bar_s_full[h]));
+                        } else {
+                            mbar_arrive(smem_u32(&sm.bar_empty[gk % NS]));
+                            if (j + 2 == n) mbar_arrive(smem_u32(&sm.bar_q_empty[h]));   // the last Q.K^T of the item
                         }
-                        if (u + 3 == n2) tc_commit(smem_u32(&sm.bar_q_empty));      // that was the last Q.K^T of the item
                     }
                 }
+                if (active) pipe_release(&sm.pipe_lock, lane);
                 __syncwarp();
+                TR(6);
+#ifdef NATS_TRACE
+                tr_acc[7] += 1;
+#endif
             }
-            g += n2;
-            if (active) { gu += n2; ++na; }
+            g += 2 * n;
+            if (active) { gt += n; ++na; }
             if (ok && lane == 0) mbar_arrive(smem_u32(&sm.bar_list_empty[slot]));
         }
+#ifdef NATS_TRACE
+        if (h == 0) { TR_DUMP(16, 8); if (tr_on) { g_trace[24] = tr_lock; g_trace[25] = tr_pv; } }
+#endif
     } else if (warp >= 4) {
         // =============================== softmax + epilogue ===============================
         asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegsHigh));
@@ -521,69 +788,84 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         const uint32_t tS = tmem + lane_addr + h * 256;
         const uint32_t tO = tmem + lane_addr + h * 256 + 128;
         const float scale = p.scale_log2;
-        uint32_t gu = 0, na = 0;                         // sub-tiles / items of this head so far
-        uint32_t rounds = 0;                             // sub-tiles done in two-head items (MUFU turn taking)
+        const bool o_wide = (reinterpret_cast<uintptr_t>(p.o) & 31u) == 0;     // 32-byte stores need a 32-byte aligned output
+        uint32_t gt = 0, na = 0;                         // tiles / items of this head so far
+        uint32_t g = 0;                                  // ring slots of all items so far (two per kept tile), as the issuers count
+        const bool releaser = (warp & 3) == 0 && lane == 0;   // one thread per head frees ring slots and the Q tile
         bool ok = true;
+        TR_DECL(10);
+#ifdef NATS_TRACE
+        unsigned long long tr_epi_ld = 0;
+#endif
         for (int ic = 0; ok; ++ic) {
             const int slot = ic & 1;
-            ok = mbar_wait(smem_u32(&sm.bar_list_full[slot]), (ic >> 1) & 1, abort_flag, p.status, kErrList);
+            ok = warp_wait(smem_u32(&sm.bar_list_full[slot]), (ic >> 1) & 1, abort_flag, p.status, kErrList);
             if (!ok) break;
             const ItemHeader hd = sm.item[slot];
             if (!hd.valid) break;
+            TR(8);
             if (h < hd.nslots) {
-                const bool pingpong = kPingPong && hd.nslots == 2;
-                const int n2 = 2 * hd.n_kept;
+                const int n = hd.n_kept;
                 const int qpos = p.q_off + hd.t * kTile + row;   // position of this thread's query row in the KV sequence
                 const int32_t* lim = p.lim + (size_t)hd.bh * p.Nc;
                 float m_ref = -INFINITY, l_sum = 0.f;
-                for (int u = 0; u < n2; ++u, ++gu) {
-                    const int entry = sm.list[slot][u >> 1];
-                    const int buf = u & 1;
-                    const int k0 = (entry & 0x7fff) * kTile + buf * kSub;   // first key column of this sub-tile
-                    const bool partial = (entry & 0x8000) != 0;
-                    // visibility bits of this row for the 64 columns of a sub-tile that is not fully visible
-                    uint32_t bits[2] = {0xffffffffu, 0xffffffffu};
+                TileWalk walk;
+                walk.init(sm.keep[slot], sm.part[slot]);
+                for (int j = 0; j < n; ++j, ++gt) {
+                    bool partial;
+                    const int k0 = walk.next(partial) * kTile;    // first key column of this tile
+                    // visibility bits of this row for the 128 columns of a tile that is not fully visible
+                    uint32_t bits[4] = {0xffffffffu, 0xffffffffu, 0xffffffffu, 0xffffffffu};
                     if (partial) {
-                        // columns this row may see: the causal prefix (and nothing past N), minus every chunk whose row limit is below it
-                        const int nvis = max(0, min(min(qpos - k0 + 1, p.Nkv - k0), kSub));
+                        // columns this row may see: the causal prefix (and nothing past Nkv), minus every chunk whose row limit is below it
+                        const int nvis = max(0, min(min(qpos - k0 + 1, p.Nkv - k0), kTile));
 #pragma unroll
-                        for (int w = 0; w < 2; ++w) bits[w] = range_mask(0, nvis, w);
-                        const int c_first = k0 / p.C, c_last = min((k0 + kSub - 1) / p.C, p.Nc - 1);
+                        for (int w = 0; w < 4; ++w) bits[w] = range_mask(0, nvis, w);
+                        const int c_first = k0 / p.C, c_last = min((k0 + kTile - 1) / p.C, p.Nc - 1);
 #pragma unroll 1
                         for (int cc = c_first; cc <= c_last; ++cc) {
                             if (qpos > lim[cc]) {
-                                const int lo = max(cc * p.C - k0, 0), hi = min((cc + 1) * p.C - k0, kSub);
+                                const int lo = max(cc * p.C - k0, 0), hi = min((cc + 1) * p.C - k0, kTile);
 #pragma unroll
-                                for (int w = 0; w < 2; ++w) bits[w] &= ~range_mask(lo, hi, w);
+                                for (int w = 0; w < 4; ++w) bits[w] &= ~range_mask(lo, hi, w);
                             }
                         }
                     }
-                    ok = mbar_wait(smem_u32(&sm.bar_s_full[h][buf]), (gu >> 1) & 1, abort_flag, p.status, kErrSFull);
+                    // S of tile j is complete; so is O += P.V of tile j - 1, which the same thread issued in front of it
+                    TR(0);
+                    ok = warp_wait(smem_u32(&sm.bar_s_full[h]), gt & 1, abort_flag, p.status, kErrSFull);
                     if (!ok) break;
                     tc_fence_after();
-                    // the score row of this thread in registers: two loads in flight, one wait
-                    uint32_t sreg[kSub];
-                    tmem_ld32(tS + buf * kSub, *reinterpret_cast<uint32_t(*)[32]>(&sreg[0]));
-                    tmem_ld32(tS + buf * kSub + 32, *reinterpret_cast<uint32_t(*)[32]>(&sreg[32]));
+                    if (releaser) {
+                        // Q.K^T of tile j is complete: this head is done with K_j and, on the item's last tile, with its Q tile
+                        mbar_arrive(smem_u32(&sm.bar_empty[(g + 2 * j) % NS]));
+                        if (j == n - 1) mbar_arrive(smem_u32(&sm.bar_q_empty[h]));
+                    }
+                    TR(1);
+                    // the score row of this thread in registers: four loads in flight, one wait
+                    uint32_t sreg[kTile];
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) tmem_ld32(tS + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&sreg[c * 32]));
                     tc_wait_ld();
+                    TR(2);
                     if (partial) {
 #pragma unroll
-                        for (int i = 0; i < kSub; ++i)
+                        for (int i = 0; i < kTile; ++i)
                             if (!((bits[i >> 5] >> (i & 31)) & 1u)) sreg[i] = 0xff800000u;      // -inf: exp2 gives exactly 0
                     }
                     float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll
-                    for (int i = 0; i < kSub; i += 4) {
-                        mx0 = fmaxf(mx0, __uint_as_float(sreg[i]));
-                        mx1 = fmaxf(mx1, __uint_as_float(sreg[i + 1]));
-                        mx2 = fmaxf(mx2, __uint_as_float(sreg[i + 2]));
-                        mx3 = fmaxf(mx3, __uint_as_float(sreg[i + 3]));
+                    for (int i = 0; i < kTile; i += 8) {
+                        mx0 = max3(mx0, __uint_as_float(sreg[i]), __uint_as_float(sreg[i + 1]));
+                        mx1 = max3(mx1, __uint_as_float(sreg[i + 2]), __uint_as_float(sreg[i + 3]));
+                        mx2 = max3(mx2, __uint_as_float(sreg[i + 4]), __uint_as_float(sreg[i + 5]));
+                        mx3 = max3(mx3, __uint_as_float(sreg[i + 6]), __uint_as_float(sreg[i + 7]));
                     }
                     const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * scale;       // scale > 0
                     // online softmax with lazy rescaling: the reference maximum only moves when the row max grew by > threshold
                     float alpha = 1.f;
                     bool need = false;
-                    if (mx > m_ref + kRescaleThreshold) {           // also true for the first visible sub-tile (m_ref = -inf)
+                    if (mx > m_ref + kRescaleThreshold) {           // also true for the first visible tile (m_ref = -inf)
                         if (m_ref != -INFINITY) {                   // a row without visible entries so far has O = 0, l = 0
                             alpha = ex2(m_ref - mx);
                             l_sum *= alpha;
@@ -591,11 +873,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                         }
                         m_ref = mx;
                     }
-                    if (u > 0 && __any_sync(0xffffffffu, need)) {
-                        // O_h is rescaled in place; the P.V of the previous sub-tile has to be complete first
-                        ok = mbar_wait(smem_u32(&sm.bar_pv_done[h]), (gu - 1) & 1, abort_flag, p.status, kErrPvDone);
-                        if (!ok) break;
-                        tc_fence_after();
+                    if (j > 0 && __any_sync(0xffffffffu, need)) {
+                        // O_h is rescaled in place (the P.V of the previous tile is complete, see above)
 #pragma unroll 1
                         for (int c = 0; c < D / 32; ++c) {
                             uint32_t r[32];
@@ -607,71 +886,120 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                         }
                     }
                     const float m_neg = (m_ref == -INFINITY) ? 0.f : -m_ref;
-                    // The warps of the two heads that sit on the same scheduler share its MUFU pipe: they take turns for the
-                    // exponentials (slot 0 first), so each runs them at the full rate while the other does its loads and maxima.
-                    if (pingpong && (h == 1 || rounds > 0)) {
-                        ok = mbar_wait(smem_u32(&sm.bar_mufu[h][warp & 3]), (h == 1 ? rounds : rounds - 1) & 1, abort_flag, p.status, kErrMufu);
-                        if (!ok) break;
-                    }
-                    // P = exp2(S * scale - m), row sum in fp32, P packed to bf16 over the first 32 columns of this score buffer
+                    TR(3);
+                    // P = exp2(S * scale - m), row sum in fp32, P packed to bf16 over the first 64 columns of S; each half
+                    // (64 keys) is published as soon as it is stored
+#if NATS_F32X2
+                    const uint64_t scale2 = pack2(scale, scale), mneg2 = pack2(m_neg, m_neg);
+                    uint64_t ls2 = pack2(0.f, 0.f);
+#else
                     float ls0 = 0.f, ls1 = 0.f;
+#endif
 #pragma unroll
-                    for (int c = 0; c < kSub / 32; ++c) {
-                        uint32_t pk[16];
+                    for (int half = 0; half < 2; ++half) {
 #pragma unroll
-                        for (int i = 0; i < 32; i += 2) {
-                            const float p0 = ex2(fmaf(__uint_as_float(sreg[c * 32 + i]), scale, m_neg));
-                            const float p1 = ex2(fmaf(__uint_as_float(sreg[c * 32 + i + 1]), scale, m_neg));
-                            ls0 += p0;
-                            ls1 += p1;
-                            pk[i / 2] = pack_bf16(p0, p1);
+                        for (int c = 0; c < 2; ++c) {
+                            uint32_t pk[16];
+                            const int base = half * 64 + c * 32;
+#pragma unroll
+                            for (int i = 0; i < 32; i += 2) {
+#if NATS_F32X2
+                                const uint64_t x2 = fma2(pack2(__uint_as_float(sreg[base + i]), __uint_as_float(sreg[base + i + 1])), scale2, mneg2);
+                                float p0, p1;
+                                if (NATS_POLY > 0 && ((i / 2) % (NATS_POLY > 0 ? NATS_POLY : 1)) == NATS_POLY - 1) {
+                                    exp2_poly2(x2, p0, p1);        // a share of the exponentials runs beside the MUFU
+                                } else {
+                                    float x0, x1;
+                                    unpack2(x2, x0, x1);
+                                    p0 = ex2(x0);
+                                    p1 = ex2(x1);
+                                }
+                                ls2 = add2(ls2, pack2(p0, p1));
+#else
+                                const float p0 = ex2(fmaf(__uint_as_float(sreg[base + i]), scale, m_neg));
+                                const float p1 = ex2(fmaf(__uint_as_float(sreg[base + i + 1]), scale, m_neg));
+                                ls0 += p0;
+                                ls1 += p1;
+#endif
+                                pk[i / 2] = pack_bf16(p0, p1);
+                            }
+                            tmem_st16(tS + half * 32 + c * 16, pk);
                         }
-                        tmem_st16(tS + buf * kSub + c * 16, pk);
+                        tc_wait_st();
+                        tc_fence_before();
+                        __syncwarp();                             // every lane's half of P is in TMEM and fenced
+                        if (lane == 0) mbar_arrive(smem_u32(&sm.bar_p_full[h][half]));
+#ifdef NATS_TRACE
+                        if (half == 0) TR(4); else TR(5);
+#endif
                     }
+#if NATS_F32X2
+                    {
+                        float a, b;
+                        unpack2(ls2, a, b);
+                        l_sum += a + b;
+                    }
+#else
                     l_sum += ls0 + ls1;
-                    if (pingpong) {
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive(smem_u32(&sm.bar_mufu[h ^ 1][warp & 3]));
-                        ++rounds;
-                    }
-                    tc_wait_st();
-                    tc_fence_before();
-                    __syncwarp();                                 // every lane's P is in TMEM and fenced
-                    if (lane == 0) mbar_arrive(smem_u32(&sm.bar_p_full[h][buf]));
+#endif
                 }
                 // epilogue: O / l -> bf16 -> global; O_h is handed back to the issuer as soon as it sits in registers
-                if (ok) ok = mbar_wait(smem_u32(&sm.bar_o_full[h]), na & 1, abort_flag, p.status, kErrOFull);
+                TR(0);
+                if (ok) ok = warp_wait(smem_u32(&sm.bar_o_full[h]), na & 1, abort_flag, p.status, kErrOFull);
+                TR(6);
                 if (ok) {
                     tc_fence_after();
                     const float inv = l_sum > 0.f ? 1.f / l_sum : 0.f;
                     const int qi = hd.t * kTile + row;           // query row
                     __nv_bfloat16* orow = p.o + (((size_t)hd.b * p.Hq + hd.head0 + h) * p.N + qi) * D;
-                    uint32_t oreg[D];
-#pragma unroll
-                    for (int c = 0; c < D / 32; ++c) tmem_ld32(tO + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&oreg[c * 32]));
-                    tc_wait_ld();
-                    tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(smem_u32(&sm.bar_o_empty[h]));
+                    constexpr int OW = D < 128 ? D : 128;          // columns of O held in registers at a time
                     if (p.lse != nullptr && qi < p.N)
                         p.lse[((size_t)hd.b * p.Hq + hd.head0 + h) * p.N + qi] = l_sum > 0.f ? m_ref + log2f(l_sum) : -INFINITY;
-                    if (qi < p.N) {
+#pragma unroll 1
+                    for (int c0 = 0; c0 < D; c0 += OW) {
+                        uint32_t oreg[OW];
 #pragma unroll
-                        for (int i = 0; i < D; i += 8) {
-                            uint4 w;
-                            w.x = pack_bf16(__uint_as_float(oreg[i]) * inv, __uint_as_float(oreg[i + 1]) * inv);
-                            w.y = pack_bf16(__uint_as_float(oreg[i + 2]) * inv, __uint_as_float(oreg[i + 3]) * inv);
-                            w.z = pack_bf16(__uint_as_float(oreg[i + 4]) * inv, __uint_as_float(oreg[i + 5]) * inv);
-                            w.w = pack_bf16(__uint_as_float(oreg[i + 6]) * inv, __uint_as_float(oreg[i + 7]) * inv);
-                            st16(orow + i, w);
+                        for (int c = 0; c < OW / 32; ++c) tmem_ld32(tO + c0 + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&oreg[c * 32]));
+                        tc_wait_ld();
+                        if (c0 + OW >= D) {                          // O_h is in registers: hand it back to the issuer
+                            tc_fence_before();
+                            __syncwarp();
+                            if (lane == 0) mbar_arrive(smem_u32(&sm.bar_o_empty[h]));
+                        }
+#ifdef NATS_TRACE
+                        { const unsigned long long t_ = clock64(); tr_epi_ld += t_ - tr_t; tr_t = t_; }
+#endif
+                        if (qi < p.N) {
+                            // a thread owns a whole output row (D * 2 bytes): 32-byte stores, one full sector each
+#pragma unroll
+                            for (int i = 0; i < OW; i += 16) {
+                                uint32_t w[8];
+#pragma unroll
+                                for (int x = 0; x < 8; ++x)
+                                    w[x] = pack_bf16(__uint_as_float(oreg[i + 2 * x]) * inv, __uint_as_float(oreg[i + 2 * x + 1]) * inv);
+                                if (o_wide) {
+                                    st32(orow + c0 + i, w);
+                                } else {
+                                    st16(orow + c0 + i, make_uint4(w[0], w[1], w[2], w[3]));
+                                    st16(orow + c0 + i + 8, make_uint4(w[4], w[5], w[6], w[7]));
+                                }
+                            }
                         }
                     }
                 }
                 ++na;
+                TR(7);
+#ifdef NATS_TRACE
+                tr_acc[9] += n;
+#endif
             }
+            g += 2 * hd.n_kept;
             __syncwarp();
             if (ok && lane == 0) mbar_arrive(smem_u32(&sm.bar_list_empty[slot]));
         }
+#ifdef NATS_TRACE
+        if (warp == 4) { TR_DUMP(0, 10); if (tr_on) g_trace[10] = tr_epi_ld; }
+#endif
     }
     // ---- teardown ----
     tc_fence_before();
@@ -735,21 +1063,23 @@ static PrefillWs prefill_ws(int B, int Hkv, int N, int C) {
     return w;
 }
 
+constexpr int kMaxDevices = 64;
+
 template <int D>
 static int launch_prefill(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const PrefillParams& p,
-                          int B, cudaStream_t st) {
-    const size_t smem = sizeof(PrefillSmem<D>) + 1024;
-    static bool attr_set = false;
-    if (!attr_set) {
-        NATS_CHECK_CUDA(cudaFuncSetAttribute(prefill_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        attr_set = true;
-    }
+                          cudaStream_t st) {
+    const size_t smem = sizeof(PrefillSmem<D>);
     int dev = 0, sms = 0;
     NATS_CHECK_CUDA(cudaGetDevice(&dev));
+    // the opt-in to more than 48 KB of dynamic shared memory is a per-device attribute of the kernel
+    static bool attr_set[kMaxDevices] = {};
+    if (dev < 0 || dev >= kMaxDevices || !attr_set[dev]) {
+        NATS_CHECK_CUDA(cudaFuncSetAttribute(prefill_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        if (dev >= 0 && dev < kMaxDevices) attr_set[dev] = true;
+    }
     NATS_CHECK_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
     NATS_CHECK_CUDA(cudaMemsetAsync(p.work_counter, 0, sizeof(int32_t), st));
     const int grid = p.total_items < sms ? p.total_items : sms;      // one persistent CTA per SM
-    (void)B;
     prefill_kernel<D><<<grid, kPrefillThreads, smem, st>>>(mq, mk, mv, p);
     NATS_CHECK_CUDA(cudaGetLastError());
     return NATS_OK;
@@ -763,20 +1093,22 @@ static int run_prefill(const void* d_q, const void* d_k, const void* d_v, void* 
                        float* d_lse = nullptr) {
     CUtensorMap mq, mk, mv;
     if (int rc = make_map(&mq, d_q, B * Hq, N, D, 128)) return rc;
-    if (int rc = make_map(&mk, d_k, B * Hkv, Nkv, D, kSub, kv_head_stride)) return rc;
-    if (int rc = make_map(&mv, d_v, B * Hkv, Nkv, D, kSub, kv_head_stride)) return rc;
+    if (int rc = make_map(&mk, d_k, B * Hkv, Nkv, D, 128, kv_head_stride)) return rc;
+    if (int rc = make_map(&mv, d_v, B * Hkv, Nkv, D, 128, kv_head_stride)) return rc;
     PrefillParams p;
     p.o = (__nv_bfloat16*)d_o; p.lse = d_lse; p.lim = lim; p.tile_max = tmax; p.tile_min = tmin; p.status = d_status;
     p.Hq = Hq; p.Hkv = Hkv; p.N = N; p.Nkv = Nkv; p.q_off = q_off; p.C = C;
     p.Nc = cdiv(Nkv, C); p.Nt = cdiv(N, kTile); p.Ntk = cdiv(Nkv, kTile);
-    p.nrep = Hq / Hkv; p.n_groups = (p.nrep + 1) / 2;
+    const int heads_per_item = D <= 128 ? 2 : 1;
+    p.nrep = Hq / Hkv; p.n_groups = (p.nrep + heads_per_item - 1) / heads_per_item;
     p.work_counter = counter;
     const long long items = (long long)B * Hkv * p.n_groups * p.Nt;
     NATS_CHECK_ARG(items <= 0x7fffffffLL - 65536, "too many work items (%lld)", items);
     p.total_items = (int)items;
     p.scale_log2 = sm_scale * 1.4426950408889634f;
-    if (D == 64) return launch_prefill<64>(mq, mk, mv, p, B, st);
-    return launch_prefill<128>(mq, mk, mv, p, B, st);
+    if (D == 64) return launch_prefill<64>(mq, mk, mv, p, st);
+    if (D == 256) return launch_prefill<256>(mq, mk, mv, p, st);
+    return launch_prefill<128>(mq, mk, mv, p, st);
 }
 
 }  // namespace nats
@@ -798,7 +1130,7 @@ static int prefill_first_call(const void* d_q, const void* d_k, const void* d_v,
     NATS_CHECK_ARG(((uintptr_t)d_q | (uintptr_t)d_k | (uintptr_t)d_v | (uintptr_t)d_o | (uintptr_t)d_workspace) % 16 == 0,
                    "q, k, v, o and the workspace must be 16-byte aligned");
     NATS_CHECK_ARG(sm_scale > 0.f, "sm_scale must be positive");
-    if (D != 64 && D != 128) return fail(NATS_ERR_UNSUPPORTED, "prefill supports head_dim 64 and 128, got %d", D);
+    if (D != 64 && D != 128 && D != 256) return fail(NATS_ERR_UNSUPPORTED, "prefill supports head_dim 64, 128 and 256, got %d", D);
     NATS_CHECK_ARG(N <= kMaxTiles * kTile, "N = %d exceeds the prefill limit %d", N, kMaxTiles * kTile);
     NATS_CHECK_ARG((long long)B <= 65535 && (long long)Hkv * ((Hq / Hkv + 1) / 2) <= 65535, "grid too large");
     const PrefillWs w = prefill_ws(B, Hkv, N, C);
@@ -852,7 +1184,7 @@ extern "C" __attribute__((visibility("default"))) int nats_b200_prefill_past_fwd
     NATS_CHECK_ARG(sm_scale > 0.f, "sm_scale must be positive");
     NATS_CHECK_ARG(t0 >= SW && t0 % C == 0 && fill >= 0 && fill < C, "tail offset %d must be a multiple of the chunk size >= the window, fill %d in [0, chunk)", t0, fill);
     NATS_CHECK_ARG(tail >= 0 && tail < SW && tail % C == 0, "ring tail %d must be a multiple of the chunk size inside the window", tail);
-    if (D != 64 && D != 128) return fail(NATS_ERR_UNSUPPORTED, "prefill supports head_dim 64 and 128, got %d", D);
+    if (D != 64 && D != 128 && D != 256) return fail(NATS_ERR_UNSUPPORTED, "prefill supports head_dim 64, 128 and 256, got %d", D);
     const long long n_kv = (long long)t0 + fill + x_len;
     NATS_CHECK_ARG(n_kv <= cache_capacity, "the cache holds %d rows, %lld are needed (the new tokens must have been appended)", cache_capacity, n_kv);
     NATS_CHECK_ARG(n_kv <= (long long)kMaxTiles * kTile, "cache + new tokens = %lld rows exceed the prefill limit %d", n_kv, kMaxTiles * kTile);
@@ -875,7 +1207,6 @@ extern "C" __attribute__((visibility("default"))) int nats_b200_prefill_past_fwd
 namespace nats {
 
 constexpr size_t kStaticScratchBytes = 1u << 20;   // 1 MiB per GPU that loads the library, held until the process exits
-constexpr int kMaxDevices = 64;
 
 // Scratch for the role metadata (row limits and per-tile max / min limits) of nats_b200_prefill_fwd_static.
 // In host code this name is only a stand-in for the symbol: the device address is obtained once per device below.
@@ -921,3 +1252,9 @@ extern "C" __attribute__((visibility("default"))) int nats_b200_prefill_fwd_stat
 }
 
 
+
+#ifdef NATS_TRACE
+extern "C" __attribute__((visibility("default"))) int nats_b200_debug_trace(unsigned long long* host_out) {
+    return cudaMemcpyFromSymbol(host_out, nats::g_trace, sizeof(unsigned long long) * 64) == cudaSuccess ? 0 : 1;
+}
+#endif
