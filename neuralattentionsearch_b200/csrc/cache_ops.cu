@@ -291,8 +291,8 @@ __global__ void __launch_bounds__(kCopyThreads) evict_compact_kernel(const Compa
     const int base = past ? p.base[bh] : p.SW / p.C;      // chunk slot of the first kept chunk of this call
     const uint4 zero = make_uint4(0, 0, 0, 0);
     int blk = blockIdx.x;
-    if (trow >= tpp) return;                              // head dims whose vector count does not divide 256
     if (blk < p.nB) {
+        if (trow >= tpp) return;                          // head dims whose vector count does not divide 256
         // section B: the last min(n_full, SW/C) complete chunks of the call go to the ring slots behind the tail (data if
         // the chunk is a sliding one, else zeros + invalid); slots the call does not reach keep what they held
         const int n_upd = min(p.n_full, p.SW / p.C);
@@ -327,45 +327,66 @@ __global__ void __launch_bounds__(kCopyThreads) evict_compact_kernel(const Compa
     // chunks of this call (slot r holds the chunk whose rank is r: ranks grow with the chunk index, so the chunk is found
     // by bisection); [len, Lcap) is zero except the tokens of the unfinished chunk at [T0, T0+rem).  Launching blocks per
     // destination instead of per source token matters: most source chunks are not kept.
+    // Step 1: one thread per destination token of the block works out where its row comes from (source row in k / v,
+    // -1: zeros, -2: leave alone), so that the bisection's chain of dependent loads is paid once per block and not in front
+    // of every copy.  Step 2: every thread loads all of its 16-byte vectors, then stores them.
+    __shared__ int s_src[kTokPerBlock];
     const int len = (int)(p.size_global[bh] + p.size_local[bh]);
     const int T0 = p.state[0];
     const int rem = p.N - p.n_full * p.C;
     const int d0 = p.SW + blk * kTokPerBlock;
-    for (int i = trow; i < kTokPerBlock; i += tpp) {
-        const int d = d0 + i;
-        if (d >= p.Lcap) break;
-        const bool in_tail = d >= T0 && d < T0 + rem;
-        if (tvec == 0) valid[d] = (d < len || in_tail) ? 1 : 0;
-        const size_t dst = (size_t)d * p.rowB + tvec;
-        if (d < len) {
-            if (d < base * p.C) {
-                if (past) {
-                    st16(ck + dst, ld16_stream(k + dst));
-                    st16(cv + dst, ld16_stream(v + dst));
+    if (tid < kTokPerBlock) {
+        const int d = d0 + tid;
+        int src = -2;
+        if (d < p.Lcap) {
+            const bool in_tail = d >= T0 && d < T0 + rem;
+            valid[d] = (d < len || in_tail) ? 1 : 0;
+            if (d < len) {
+                if (d < base * p.C) {
+                    if (past) src = d;
+                } else {
+                    // the chunk of rank r: the smallest index up to which r + 1 chunks are kept
+                    const int r = d / p.C - base;
+                    int lo = r, hi = p.n_full - 1;                 // it cannot sit in front of index r
+                    while (lo < hi) {
+                        const int mid = (lo + hi) >> 1;
+                        const int v = rank[mid];
+                        const int kept_upto = v >= 0 ? v + 1 : -1 - v;         // kept chunks in [0, mid]
+                        if (kept_upto >= r + 1) hi = mid; else lo = mid + 1;
+                    }
+                    src = p.src_off + lo * p.C + d % p.C;
                 }
-                continue;
+            } else if (in_tail) {
+                src = p.src_off + p.n_full * p.C + (d - T0);
+            } else {
+                src = -1;
             }
-            // the chunk of rank r: the smallest index up to which r + 1 chunks are kept
-            const int r = d / p.C - base;
-            int lo = r, hi = p.n_full - 1;                 // it cannot sit in front of index r
-            while (lo < hi) {
-                const int mid = (lo + hi) >> 1;
-                const int v = rank[mid];
-                const int kept_upto = v >= 0 ? v + 1 : -1 - v;         // kept chunks in [0, mid]
-                if (kept_upto >= r + 1) hi = mid; else lo = mid + 1;
-            }
-            const size_t src = (size_t)(p.src_off + lo * p.C + d % p.C) * p.rowB + tvec;
-            st16(ck + dst, ld16_stream(k + src));
-            st16(cv + dst, ld16_stream(v + src));
-            continue;
         }
-        if (in_tail) {
-            const size_t src = (size_t)(p.src_off + p.n_full * p.C + (d - T0)) * p.rowB + tvec;
-            st16(ck + dst, ld16_stream(k + src));
-            st16(cv + dst, ld16_stream(v + src));
-        } else {
-            st16(ck + dst, zero);
-            st16(cv + dst, zero);
+        s_src[tid] = src;
+    }
+    __syncthreads();
+    if (trow >= tpp) return;                              // head dims whose vector count does not divide 256
+    constexpr int kBatch = 4;
+    for (int i0 = trow; i0 < kTokPerBlock; i0 += kBatch * tpp) {
+        uint4 a[kBatch], b[kBatch];
+        int sr[kBatch];
+#pragma unroll
+        for (int u = 0; u < kBatch; ++u) {
+            const int i = i0 + u * tpp;
+            sr[u] = i < kTokPerBlock ? s_src[i] : -2;
+            a[u] = b[u] = zero;
+            if (sr[u] >= 0) {
+                const size_t src = (size_t)sr[u] * p.rowB + tvec;
+                a[u] = ld16_stream(k + src);
+                b[u] = ld16_stream(v + src);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < kBatch; ++u) {
+            if (sr[u] == -2) continue;
+            const size_t dst = (size_t)(d0 + i0 + u * tpp) * p.rowB + tvec;
+            st16(ck + dst, a[u]);
+            st16(cv + dst, b[u]);
         }
     }
 }
