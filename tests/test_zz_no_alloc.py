@@ -33,23 +33,32 @@ def test_static_scratch_prefill_equals_regular_prefill_twice():
     k = (torch.randn(B, Hkv, N, D, generator=g) * 0.5).to(dev).bfloat16()
     v = (torch.randn(B, Hkv, N, D, generator=g) * 0.5).to(dev).bfloat16()
     nc = -(-N // C)
-    free_before = torch.cuda.mem_get_info(dev)[0]
+    # everything the calls touch exists before the memory reading is taken: inputs, outputs, references
+    cases = []
     for seed in (1, 2):
         roles = _roles(B, Hkv, nc, seed).to(dev)
-        ref = prefill_attention(q, k, v, roles, C, SW)
         kept_ref = torch.zeros(B, Hkv, dtype=torch.int64, device=dev)
-        prefill_attention(q, k, v, roles, C, SW, kept_tiles=kept_ref)
-        o = torch.full_like(q, float('nan'))
-        kept = torch.zeros(B, Hkv, dtype=torch.int64, device=dev)
-        torch.cuda.synchronize()
+        ref = prefill_attention(q, k, v, roles, C, SW, kept_tiles=kept_ref)
+        cases.append((seed, roles, ref, kept_ref, torch.full_like(q, float('nan')), torch.zeros(B, Hkv, dtype=torch.int64, device=dev)))
+    status = status_word(dev)
+    stream = torch.cuda.current_stream(dev).cuda_stream
+
+    def static_call(roles, o, kept):
         _lib.call('nats_b200_prefill_fwd_static', q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), roles.data_ptr(),
-                  B, Hq, Hkv, N, D, C, SW, D ** -0.5, kept.data_ptr(), status_word(dev).data_ptr(),
-                  torch.cuda.current_stream(dev).cuda_stream)
+                  B, Hq, Hkv, N, D, C, SW, D ** -0.5, kept.data_ptr(), status.data_ptr(), stream)
+
+    warm = torch.empty_like(q)
+    static_call(cases[0][1], warm, torch.zeros(B, Hkv, dtype=torch.int64, device=dev))     # the first call looks up the scratch address
+    torch.cuda.synchronize()
+    for seed, roles, ref, kept_ref, o, kept in cases:
+        free_before = torch.cuda.mem_get_info(dev)[0]
+        static_call(roles, o, kept)
+        torch.cuda.synchronize()
+        # the call allocated nothing on the device, neither from the driver nor through torch
+        assert torch.cuda.mem_get_info(dev)[0] == free_before
         check_status(dev)
         assert torch.equal(o, ref), f'seed {seed}: max diff {(o.float() - ref.float()).abs().max().item()}'
         assert torch.equal(kept, kept_ref)
-    # nothing was allocated on the device by the calls (torch's own pool does not grow for them either)
-    assert torch.cuda.mem_get_info(dev)[0] >= free_before - (64 << 20)
 
 
 def test_static_scratch_rejects_shapes_beyond_its_size():
