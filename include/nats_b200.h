@@ -10,7 +10,14 @@
  *   - ``stream`` is a cudaStream_t passed as void*; work is only enqueued, never synchronised;
  *   - the return value is 0 on success, else one of NATS_ERR_*; nats_b200_last_error() gives the text;
  *   - kernels that wait on hardware barriers bound every wait and report a time-out through the
- *     caller's device status word (0 = ok) instead of spinning forever.
+ *     caller's device status word (0 = ok) instead of spinning forever; a non-zero word also makes every
+ *     later prefill launch return at once, so read the word back (after the stream has finished) before
+ *     d_o is used, and clear it before the next call;
+ *   - the library reads the CURRENT device (SM count, per-device kernel attributes, built-in scratch): make the
+ *     device that owns the pointers and the stream current before a call;
+ *   - host threads: calls are thread safe once a device has been used; the first call of an entry point on a
+ *     device initialises per-device state without locking, so let one host thread make it before others call
+ *     concurrently.
  *
  * File paths in the comments below are relative to the reference project root.
  */
@@ -26,7 +33,7 @@ extern "C" {
 
 #define NATS_OK               0
 #define NATS_ERR_INVALID_ARG  1   /* shape / alignment / null pointer */
-#define NATS_ERR_UNSUPPORTED  2   /* valid for the reference, not built here (e.g. head_dim 256) */
+#define NATS_ERR_UNSUPPORTED  2   /* valid for the reference, not built here (e.g. head_dim 16 or 32 at this level) */
 #define NATS_ERR_CUDA         3   /* a CUDA runtime / driver call failed */
 #define NATS_ERR_WORKSPACE    4   /* workspace too small */
 
@@ -65,7 +72,8 @@ size_t nats_b200_prefill_workspace_bytes(int B, int Hkv, int N, int C);
  * nats_chunk_attention forward (src/nats/models/transformer/triton/nats_chunk_attention.py:1154-1185) and the
  * eager pair generate_mask + scaled_dot_product_attention
  * (src/nats/models/transformer/attention/nats_chunk_attention.py:130-142).  The mask is the eager one.
- *   d_q [B,Hq,N,D], d_k,d_v [B,Hkv,N,D], d_o [B,Hq,N,D]  bf16, 16-byte aligned; D in {64,128}; Hq % Hkv == 0
+ *   d_q [B,Hq,N,D], d_k,d_v [B,Hkv,N,D], d_o [B,Hq,N,D]  bf16, 16-byte aligned (d_o 32-byte aligned is faster);
+ *   D in {64,128,256} (16 and 32 run zero-padded to 64 through the Python wrapper); Hq % Hkv == 0
  *   d_roles uint8 [B,Hkv,ceil(N/C)];  SW % C == 0;  N <= 524288
  *   d_workspace: nats_b200_prefill_workspace_bytes bytes;  d_kept_tiles int64 [B,Hkv] or NULL
  *   d_status: one int32, must be 0 on entry; non-zero afterwards means a bounded wait gave up and d_o is invalid

@@ -53,8 +53,11 @@ class BaseNAtSChunkAttentionLayer(nn.Module):
         self.dropout = dropout
         if n_msks is None:
             n_msks = self.n_kv_heads
-        if n_msks != self.n_kv_heads:
-            raise ValueError('the kernels take one role per kv-head: n_msks must equal n_kv_heads')
+        if self.n_kv_heads % n_msks != 0:
+            # base reference: mask head m covers n_heads // n_msks query heads (transformer/utils.py:35-46); the kernels
+            # share one kept-tile list among the query heads of a kv-head, so a mask head must cover whole kv-heads
+            raise ValueError(f'n_msks = {n_msks} must divide n_kv_heads = {self.n_kv_heads}: the kernels take one role per '
+                             'kv-head (a role head shared by several kv-heads is expanded, one finer than a kv-head is not built)')
         if n_options != 3:
             raise ValueError('three roles (global, local, sliding window) are supported')
         self.proj_layer = nn.Linear(dim, n_msks * n_options, bias=False)
@@ -85,7 +88,10 @@ class BaseNAtSChunkAttentionLayer(nn.Module):
         if start_pos < self.chunk_size:
             index[:, 0].fill_(0)                             # the first chunk is the attention sink
         samples = torch.zeros_like(logit).scatter_(-1, index, 1.0)
-        return samples.transpose(1, 2).contiguous()          # [B, Hkv, Nc, 3]
+        samples = samples.transpose(1, 2)                    # [B, n_msks, Nc, 3]
+        if self.n_msks != self.n_kv_heads:                   # a role head shared by several kv-heads: one copy per kv-head
+            samples = samples.repeat_interleave(self.n_kv_heads // self.n_msks, 1)
+        return samples.contiguous()                          # [B, Hkv, Nc, 3]
 
     def _sample_for_token_info_values_inference(self, x: torch.Tensor, start_pos: int, cache: NAtSCache) -> torch.Tensor:
         x_len = x.shape[1]

@@ -296,7 +296,7 @@ class NAtSChunkLayerCache:
         self._t0_bound += C
         self._t0_exact = None
         self._pending = None
-        if self._t0_bound - self._t0_synced >= 8 * C:
+        if self._t0_bound - self._t0_synced >= max(8 * C, 512):
             self._t0()        # the bound drifts up when chunks are dropped: refresh it now and then (one small read)
 
     def _evict_after_continuation(self):

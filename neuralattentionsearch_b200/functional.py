@@ -21,7 +21,9 @@ import torch
 from . import _lib
 
 ROLE_GLOBAL, ROLE_LOCAL, ROLE_SLIDING = 0, 1, 2
-PREFILL_HEAD_DIMS = (64, 128)
+PREFILL_HEAD_DIMS = (64, 128, 256)     # head dims the prefill kernel is built for (256: one query head per work item)
+PADDED_HEAD_DIMS = (16, 32)            # run zero-padded to 64 (first call only)
+REFERENCE_HEAD_DIMS = (16, 32, 64, 128, 256)      # what the reference's Triton entry point accepts (nats_flashattn_fwd.py:633-634)
 
 _status: dict[int, torch.Tensor] = {}
 _workspaces: dict[tuple, torch.Tensor] = {}
@@ -53,6 +55,16 @@ def _need_cuda(*tensors: torch.Tensor) -> torch.device:
         if t.device != dev:
             raise ValueError('all tensors must live on the same device')
     return dev
+
+
+def _check_head_dim(D: int, padded_ok: bool = True) -> None:
+    """One clear error, before anything is launched, for head dims this build does not cover."""
+    ok = PREFILL_HEAD_DIMS + (PADDED_HEAD_DIMS if padded_ok else ())
+    if D not in ok:
+        raise NotImplementedError(
+            f'head_dim {D} is not built: the prefill kernel covers {PREFILL_HEAD_DIMS}' +
+            (f', {PADDED_HEAD_DIMS} run zero-padded' if padded_ok else ' for calls over an existing cache') +
+            f' (the reference accepts {REFERENCE_HEAD_DIMS})')
 
 
 def status_word(device: torch.device) -> torch.Tensor:
@@ -178,16 +190,26 @@ def prefill_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, roles: 
     nc = -(-N // chunk_size)
     if roles.shape != (B, Hkv, nc) or roles.dtype != torch.uint8:
         raise ValueError(f'roles must be uint8 [{B},{Hkv},{nc}], got {roles.dtype} {tuple(roles.shape)}')
+    _check_head_dim(D)
+    scale = (1.0 / math.sqrt(D)) if sm_scale is None else float(sm_scale)
     qb, kb, vb = _as_bf16(q), _as_bf16(k), _as_bf16(v)
+    if D in PADDED_HEAD_DIMS:
+        # narrow heads run in the 64-wide kernel on zero-padded copies: the scores are unchanged by zero columns of q and
+        # k, the extra output columns are zero and dropped (the scale still comes from the real head_dim)
+        if out is not None:
+            raise ValueError(f'out= is not supported for head_dim {D}')
+        pad = (0, 64 - D)
+        qb, kb, vb = (torch.nn.functional.pad(t, pad) for t in (qb, kb, vb))
     if out is not None and (out.shape != qb.shape or out.dtype != torch.bfloat16 or not out.is_contiguous()):
         raise ValueError('out must be a contiguous bf16 tensor shaped like q')
     o = torch.empty_like(qb) if out is None else out
     lib = _lib.lib()
     nbytes = lib.nats_b200_prefill_workspace_bytes(B, Hkv, N, chunk_size)
     ws = _workspace('prefill', dev, nbytes)
-    scale = (1.0 / math.sqrt(D)) if sm_scale is None else float(sm_scale)
-    _call(dev, 'nats_b200_prefill_fwd', _p(qb), _p(kb), _p(vb), _p(o), _p(roles.contiguous()), B, Hq, Hkv, N, D,
+    _call(dev, 'nats_b200_prefill_fwd', _p(qb), _p(kb), _p(vb), _p(o), _p(roles.contiguous()), B, Hq, Hkv, N, qb.shape[-1],
               chunk_size, sliding_window, scale, _p(ws), ws.numel(), _p(kept_tiles), _p(status_word(dev)), _stream(dev))
+    if D in PADDED_HEAD_DIMS:
+        o = o[..., :D].contiguous()
     return o if q.dtype == torch.bfloat16 else o.to(q.dtype)
 
 
@@ -307,7 +329,7 @@ def nats_prefill(q, k, v, end_seqs_idx, sliding_tokens, sm_scale,
             mask = (kpos[None, :] <= qpos[:, None])[None, None] & (qpos[None, None, :, None] <= lim_tok[:, :, None, :])
         return o, mask
     assert q.shape[-1] == k.shape[-1] == v.shape[-1]
-    assert q.shape[-1] in {16, 32, 64, 128, 256}
+    assert q.shape[-1] in set(REFERENCE_HEAD_DIMS)
     assert k.shape[2] == q.shape[2]
     assert q.shape[1] == k.shape[1] * n_rep
     roles = roles_from_end_seqs(end_seqs_idx, sliding_tokens)
@@ -337,6 +359,7 @@ def nats_chunk_attention_fwd(q, k, v, seq_info, end_seqs_idx, causal, sm_scale, 
     dev = _need_cuda(q, k, v, roles)
     B, Hq, N, D = q.shape
     Hkv = k.shape[1]
+    _check_head_dim(D, padded_ok=False)
     qb, kb, vb = _as_bf16(q), _as_bf16(k), _as_bf16(v)
     o = torch.empty_like(qb)
     lse = torch.empty(B, Hq, N, dtype=torch.float32, device=dev)
@@ -429,6 +452,7 @@ def prefill_attention_past(q: torch.Tensor, cache_k: torch.Tensor, cache_v: torc
             raise ValueError('the cache must be bf16 [B,Hkv,>=t0+fill+x_len,D], dense or a [:, :, :n] view of a dense buffer')
     if valid.dtype != torch.uint8 or valid.stride(2) != 1 or valid.stride(0) != Hkv * valid.stride(1):
         raise ValueError('valid must be uint8 [B,Hkv,>=SW] with contiguous rows')
+    _check_head_dim(D, padded_ok=False)
     qb = _as_bf16(q)
     o = torch.empty_like(qb)
     lib = _lib.lib()

@@ -49,7 +49,7 @@ def test_argument_errors_do_not_need_a_gpu(lib):
     one = ctypes.c_void_p(256)          # never dereferenced: the checks fail first
     rc = lib.nats_b200_prefill_fwd(one, one, one, one, one, 1, 4, 2, 128, 128, 16, 60, 0.1, one, 1 << 20, None, one, None)
     assert rc == 1 and b'multiple' in lib.nats_b200_last_error()
-    rc = lib.nats_b200_prefill_fwd(one, one, one, one, one, 1, 4, 2, 128, 256, 16, 64, 0.1, one, 1 << 20, None, one, None)
+    rc = lib.nats_b200_prefill_fwd(one, one, one, one, one, 1, 4, 2, 128, 96, 16, 64, 0.1, one, 1 << 20, None, one, None)
     assert rc == 2 and b'head_dim' in lib.nats_b200_last_error()
     rc = lib.nats_b200_prefill_fwd(one, one, one, one, one, 1, 4, 2, 128, 128, 16, 64, 0.1, one, 16, None, one, None)
     assert rc == 4

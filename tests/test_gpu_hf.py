@@ -176,3 +176,39 @@ def test_llama3_8b_shaped_decoder_end_to_end():
         assert torch.equal(lc.valid_tokens[:, :, SW:lc.n_ctx_data].sum(-1), want)
         fractions.append((lc.size_global_kv + lc.size_local_kv - SW).float().mean().item() / N)
     assert max(fractions) < 0.9 and min(fractions) >= 0.0
+
+
+def test_patched_mistral_segments_match_one_call():
+    """The Mistral patch (hf/mistral_nats_chunk.py: same structure as the Llama one) on a small random-init Mistral:
+    the hidden states of one call equal those of the same tokens fed in segments and single steps, every layer's cache holds
+    what its sizes say, and greedy decoding on top stays finite."""
+    from transformers import MistralConfig, MistralForCausalLM
+    from neuralattentionsearch_b200 import NAtSCache, check_status
+    from neuralattentionsearch_b200.hf import TransformerArgs, enable_mistral_nats_chunk_eval
+    C, SW, N = 16, 64, 300
+    torch.manual_seed(4)
+    cfg = MistralConfig(hidden_size=256, intermediate_size=512, num_hidden_layers=2, num_attention_heads=4,
+                        num_key_value_heads=2, head_dim=64, vocab_size=512, max_position_embeddings=8192, sliding_window=None)
+    model = MistralForCausalLM(cfg).to(dev()).bfloat16().eval()
+    enable_mistral_nats_chunk_eval(model, TransformerArgs(n_msks=2, chunk_size=C, local_seq_max_length=SW))
+    for layer in model.model.layers:
+        layer.self_attn.proj_layer.weight.data.normal_(0, 0.5)
+    ids = torch.randint(0, 512, (2, N), device=dev())
+    with torch.no_grad():
+        cache = NAtSCache(SW, C)
+        h_one = model.model(input_ids=ids, past_key_values=cache, use_cache=True).last_hidden_state
+        cache2 = NAtSCache(SW, C)
+        outs, pos = [], 0
+        for n in [130, 100, 1, 1, 68]:
+            outs.append(model.model(input_ids=ids[:, pos:pos + n], past_key_values=cache2, use_cache=True).last_hidden_state)
+            pos += n
+        out = model(input_ids=ids[:, -1:], past_key_values=cache, use_cache=True)
+    check_status(dev())
+    assert torch.isfinite(out.logits.float()).all()
+    h_seg = torch.cat(outs, 1)
+    err = (h_seg.float() - h_one.float()).abs()
+    assert err.mean().item() / h_one.float().abs().mean().item() < 2e-2, err.mean().item()
+    for a, b in zip(cache.cache_model, cache2.cache_model):
+        assert torch.equal(a.size_global_kv, b.size_global_kv) and torch.equal(a.size_local_kv, b.size_local_kv)
+        roles = model.model.layers[a.layer_id].self_attn.token_states
+        assert roles is not None

@@ -467,7 +467,7 @@ def test_token_granular_prefill_matches_reference_cache(name):
                                lc.valid_tokens.cpu().numpy(), lc.cache_k.float().cpu().numpy(), lc.cache_v.float().cpu().numpy())
 
 
-@pytest.mark.parametrize('name', ['tokdec_tiny', 'tokdec_k64'])
+@pytest.mark.parametrize('name', ['tokdec_k64'])          # the decode kernel is built for head_dim 64 and 128
 def test_token_granular_decode_state_at_reference_update_points(name):
     """chunk_size 1, single tokens: right after each of the reference's batched updates (every 16 steps) the cache here
     holds the reference's sizes, extent and kept rows bit for bit, and the step that follows gives the reference's output."""
@@ -823,3 +823,99 @@ def test_static_decode_step_equals_the_regular_one_and_replays_from_a_cuda_graph
     check_status(dev())
     assert torch.equal(lc.size_global_kv, ref_lc.size_global_kv) and torch.equal(lc.size_local_kv, ref_lc.size_local_kv)
     assert (lc.n_ctx_data, lc.chunk_fill_size, lc.sliding_queue_tail) == (ref_lc.n_ctx_data, ref_lc.chunk_fill_size, ref_lc.sliding_queue_tail)
+
+
+def test_a_raised_status_word_stops_the_prefill_and_is_reported():
+    """The error path of the bounded waits, exercised without making a wait run out: with the status word already
+    non-zero (what a timed-out wait of an earlier launch leaves behind) every CTA returns before it touches its output,
+    check_status raises and clears the word, and the next launch is correct."""
+    from neuralattentionsearch_b200 import _lib, check_status, prefill_attention
+    from neuralattentionsearch_b200.functional import status_word
+    B, Hq, Hkv, N, D, C, SW = 1, 4, 2, 512, 128, 32, 128
+    roles = torch.from_numpy(orc.make_roles(B, Hkv, N // C, 0.1, 0.3, seed=3)).to(dev())
+    q, k, v = inputs(B, Hq, Hkv, N, D, seed=8)
+    qd, kd, vd = (t.to(dev()).bfloat16() for t in (q, k, v))
+    good = prefill_attention(qd, kd, vd, roles, C, SW)
+    check_status(dev())
+    status_word(dev()).fill_(7)
+    out = torch.full_like(qd, 123.0)
+    prefill_attention(qd, kd, vd, roles, C, SW, out=out)
+    torch.cuda.synchronize()
+    assert bool((out == 123.0).all())                       # no CTA started
+    with pytest.raises(_lib.NatsB200Error, match='bounded wait'):
+        check_status(dev())
+    check_status(dev())                                     # cleared
+    again = prefill_attention(qd, kd, vd, roles, C, SW)
+    check_status(dev())
+    assert torch.equal(again, good)
+
+
+@pytest.mark.skipif(torch.cuda.is_available() and torch.cuda.device_count() < 2, reason='needs two GPUs in one process')
+def test_second_device_in_the_same_process():
+    """Prefill, eviction and decode on cuda:1 after cuda:0 in one process, with cuda:0 still the current device: kernel
+    attributes are set per device and every call makes the tensors' device current."""
+    from neuralattentionsearch_b200 import check_status, prefill_attention
+    from neuralattentionsearch_b200.cache import NAtSChunkLayerCache
+    B, Hq, Hkv, N, D, C, SW = 1, 4, 2, 512, 128, 32, 128
+    roles_np = orc.make_roles(B, Hkv, N // C, 0.1, 0.3, seed=3)
+    q, k, v = inputs(B, Hq, Hkv, N, D, seed=8)
+    ref = orc.prefill_attention(q, k, v, roles_np, C, SW)
+    outs = []
+    for idx in (0, 1):
+        d = torch.device('cuda', idx)
+        assert torch.cuda.current_device() == 0
+        qd, kd, vd = (t.to(d).bfloat16() for t in (q, k, v))
+        o = prefill_attention(qd, kd, vd, torch.from_numpy(roles_np).to(d), C, SW)
+        check_status(d)
+        assert_close_attn(o, ref, f'cuda:{idx}')
+        lc = NAtSChunkLayerCache(B, Hkv, SW, chunk_size=C, device=d)
+        lc.update(kd, vd, orc.onehot_from_roles(roles_np).to(d))
+        lc.post_update(N)
+        q1, k1, v1 = inputs(B, Hq, Hkv, 1, D, seed=9)
+        lc.update(k1.to(d).bfloat16(), v1.to(d).bfloat16(), orc.onehot_from_roles(np.zeros((B, Hkv, 1), np.uint8)).to(d), fused=True)
+        o1 = lc.decode_attention(q1.to(d).bfloat16())
+        lc.post_update(1)
+        outs.append((o.cpu(), o1.cpu(), lc.size_global_kv.cpu(), lc.size_local_kv.cpu()))
+    for a, b in zip(*outs):
+        assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize('D', [16, 32])
+def test_narrow_head_dims_run_zero_padded(D):
+    """head_dim 16 and 32 (accepted by the reference's entry point) through the 64-wide kernel."""
+    from neuralattentionsearch_b200 import check_status, nats_prefill
+    B, Hq, Hkv, N, C, SW = 2, 4, 2, 333, 8, 32
+    roles = orc.make_roles(B, Hkv, -(-N // C), 0.1, 0.3, seed=D)
+    q, k, v = inputs(B, Hq, Hkv, N, D, seed=D + 1)
+    fill = torch.from_numpy(orc.next_global_index(roles)).to(dev())
+    sliding = torch.from_numpy((roles == 2).astype(np.float32)).to(dev())
+    o, _ = nats_prefill(q.to(dev()).bfloat16(), k.to(dev()).bfloat16(), v.to(dev()).bfloat16(), fill, sliding, D ** -0.5,
+                        nats_chunk_size=C, n_rep=Hq // Hkv, local_seq_max_length=SW)
+    check_status(dev())
+    assert o.shape == (B, Hq, N, D)
+    # the last chunk counts as global for the next-global index (nats_prefill takes roles in that form)
+    roles_in = roles.copy()
+    roles_in[..., -1][roles_in[..., -1] == 1] = 0
+    assert_close_attn(o, orc.prefill_attention(q, k, v, roles_in, C, SW), f'head_dim {D}')
+
+
+@pytest.mark.parametrize('B,Hq,Hkv,N,C,SW', [(1, 4, 2, 700, 16, 64), (2, 3, 3, 300, 128, 256)])
+def test_head_dim_256(B, Hq, Hkv, N, C, SW):
+    """head_dim 256 (the widest the reference's entry point accepts): one query head per work item, O fills the
+    accumulator columns two heads use otherwise."""
+    from neuralattentionsearch_b200 import check_status, prefill_attention
+    D = 256
+    roles = orc.make_roles(B, Hkv, -(-N // C), 0.1, 0.3, seed=N)
+    q, k, v = inputs(B, Hq, Hkv, N, D, seed=N + 1, sigma=0.5)
+    o = prefill_attention(q.to(dev()).bfloat16(), k.to(dev()).bfloat16(), v.to(dev()).bfloat16(),
+                          torch.from_numpy(roles).to(dev()), C, SW)
+    check_status(dev())
+    assert_close_attn(o, orc.prefill_attention(q, k, v, roles, C, SW), 'head_dim 256')
+
+
+def test_unsupported_head_dim_is_refused_before_any_launch():
+    from neuralattentionsearch_b200 import prefill_attention
+    q = torch.zeros(1, 2, 128, 96, device=dev(), dtype=torch.bfloat16)
+    roles = torch.zeros(1, 2, 8, dtype=torch.uint8, device=dev())
+    with pytest.raises(NotImplementedError, match='head_dim 96'):
+        prefill_attention(q, q, q, roles, 16, 64)

@@ -65,3 +65,18 @@ def test_hf_forward_roles_match_reference(name):
             cache.fill = pre
             info = hf.sample_token_states_info(module, xs[i], cache, pos)
             assert np.array_equal(info.numpy(), ref.astype(np.float32)), f'call {i} (fill {pre}, start {pos})'
+
+
+def test_role_head_shared_by_several_kv_heads_is_expanded():
+    """n_msks < n_kv_heads: every mask head's role is used by the kv-heads it covers (query heads i use mask
+    i // (n_heads // n_msks), transformer/utils.py:35-46); a mask head finer than a kv-head is refused."""
+    torch.manual_seed(0)
+    layer = LlamaNAtSChunkAttentionLayer(dim=64, n_heads=8, n_kv_heads=4, n_msks=2, local_seq_max_length=32, chunk_size=8).eval()
+    cache = _FillCache(32, 8)
+    with torch.no_grad():
+        info = layer._sample_for_token_info_values_inference(torch.randn(2, 64, 64), 0, cache)
+    assert tuple(info.shape) == (2, 4, 8, 3)
+    assert torch.equal(info[:, 0], info[:, 1]) and torch.equal(info[:, 2], info[:, 3])
+    assert bool((info.sum(-1) == 1).all())
+    with pytest.raises(ValueError, match='n_msks'):
+        LlamaNAtSChunkAttentionLayer(dim=64, n_heads=8, n_kv_heads=2, n_msks=4)
