@@ -524,7 +524,7 @@ def run_sustained_leg(w, device, rank, seconds, q, k, v, roles, peaks):
     return out
 
 
-EVICT_LARGE = dict(B=32, Hkv=8, D=128, N=16384, C=128, SW=1024, p_global=0.04, p_local=0.12, seed=5)
+EVICT_LARGE = dict(B=32, Hkv=8, D=128, N=16384, C=128, SW=1024, p_global=0.07, p_local=0.20, seed=5)   # ~10 % of the tokens retained
 
 
 def run_eviction_large_leg(device, peaks, steps=5):
@@ -638,30 +638,32 @@ def run_decoder_leg(dc, device, rank, world, barrier):
     g = torch.Generator(device=device).manual_seed(100 + rank)
     gc = torch.Generator(device=device).manual_seed(99)                       # the calibration pass is the same on every rank
     C, SW, N = dc['C'], dc['SW'], dc['prompt']
+    target = torch.tensor([dc['p_global'], dc['p_local']], device=device)
+
+    def fit_bias(module, args_, kwargs_):
+        """Runs in front of a layer's attention during the calibration pass: fits the layer's role biases to the chunk
+        features that arrive, so that every later layer sees hidden states made under fitted roles."""
+        x = (kwargs_['hidden_states'] if 'hidden_states' in kwargs_ else args_[0]).float()
+        pooled = x.unflatten(1, (-1, C)).mean(2).flatten(0, 1)                    # [chunks, hidden]
+        wgt = module.proj_layer.weight
+        wv = wgt.view(cfg.num_key_value_heads, 3, -1)
+        wv[:, :, 0] = 0
+        z = (pooled @ wgt.float().T).view(-1, cfg.num_key_value_heads, 3)       # logits without the bias column
+        f0 = pooled[:, 0].mean()
+        bias = torch.zeros(3, device=device)
+        for _ in range(80):
+            r = (z + bias).argmax(-1)
+            frac = torch.stack([(r == 0).float().mean(), (r == 1).float().mean()]).clamp_min(1e-4)
+            bias[:2] += 0.5 * z.std() * (target.log() - frac.log())
+        wv[:, 0, 0] = (bias[0] / f0).to(wgt.dtype)
+        wv[:, 1, 0] = (bias[1] / f0).to(wgt.dtype)
+
     with torch.no_grad():
-        ids = torch.randint(0, cfg.vocab_size, (2, 8192), device=device, generator=gc)
-        feats = []
-        hooks = [layer.self_attn.register_forward_pre_hook(
-            lambda m, a, kw: feats.append((kw['hidden_states'] if 'hidden_states' in kw else a[0]).float()), with_kwargs=True)
-            for layer in model.model.layers]
+        ids = torch.randint(0, cfg.vocab_size, (2, N), device=device, generator=gc)
+        hooks = [layer.self_attn.register_forward_pre_hook(fit_bias, with_kwargs=True) for layer in model.model.layers]
         model(input_ids=ids, past_key_values=NAtSCache(SW, C), use_cache=True, logits_to_keep=1)
         for h in hooks:
             h.remove()
-        target = torch.tensor([dc['p_global'], dc['p_local']], device=device)
-        for layer, x in zip(model.model.layers, feats):
-            pooled = x.unflatten(1, (-1, C)).mean(2).flatten(0, 1)                # [chunks, hidden]
-            wgt = layer.self_attn.proj_layer.weight
-            z = (pooled @ wgt.float().T).view(-1, cfg.num_key_value_heads, 3)   # logits without the bias column
-            f0 = pooled[:, 0].mean()
-            bias = torch.zeros(3, device=device)
-            for _ in range(60):                                                 # fit the two free biases to the requested mix
-                r = (z + bias).argmax(-1)
-                frac = torch.stack([(r == 0).float().mean(), (r == 1).float().mean()]).clamp_min(1e-4)
-                bias[:2] += 0.5 * z.std() * (target.log() - frac.log())
-            wv = wgt.view(cfg.num_key_value_heads, 3, -1)
-            wv[:, 0, 0] = (bias[0] / f0).to(wgt.dtype)
-            wv[:, 1, 0] = (bias[1] / f0).to(wgt.dtype)
-        del feats
     torch.cuda.synchronize(device)
 
     pre_ms, dec_ms = 0.0, 0.0
@@ -717,10 +719,11 @@ def main():
     ap.add_argument('--decoder-batch', type=int, default=DECODER['batch'], help='sequences of the decoder leg over all GPUs')
     ap.add_argument('--decoder-steps', type=int, default=DECODER['steps'])
     ap.add_argument('--sustained-seconds', type=float, default=2.0)
-    ap.add_argument('--case', default='full', choices=['full', 'small', 'long'],
+    ap.add_argument('--case', default='full', choices=['full', 'small', 'long', 'evict'],
                     help="'small' = a quarter of the heads / of the decode batch: the profiling case (inputs still exceed L2); "
                          "'long' = the 131072-token stress configuration (batch 2, window 4096, ~2 % global / 8 % local), "
-                         "prefill + eviction only; neither line is the benchmark value")
+                         "prefill + eviction only; 'evict' = only the large eviction leg at a quarter of its batch (the profiling "
+                         "case of the compaction kernel); none of these lines is the benchmark value")
     args = ap.parse_args()
     if args.case == 'small':
         WORKLOAD.update(Hq=8, Hkv=2)
@@ -746,6 +749,16 @@ def main():
         config = dict(config, workload='LONG-CONTEXT STRESS CASE (not the benchmark value): prefill 131072 + eviction, B2 x 32q/8kv heads, '
                                        'head_dim 128, window 4096, chunk 128, roles 2/8/90 % global/local/sliding; two sequences per GPU',
                       l2='inputs larger than L2 (q+k+v+o = 5.4 GB per step)')
+
+    if args.case == 'evict':
+        device = torch.device('cuda', local_rank)
+        torch.cuda.set_device(device)
+        EVICT_LARGE.update(B=8)
+        r = run_eviction_large_leg(device, load_peaks(), steps=args.steps)
+        print(json.dumps(dict(metric='eviction GB/s (kept tokens and ring, K and V, read + write)', value=r['gbs'], unit='GB/s',
+                              n_gpus=1, steps=args.steps, warmup=2, config=dict(workload='PROFILING CASE (not a benchmark value): ' + r['shape'].replace('B32', 'B8')),
+                              eviction_large=r)))
+        return
 
     if args.impl == 'reference':
         if rank != 0:
