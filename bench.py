@@ -599,7 +599,7 @@ def run_copy_floor_leg(hq, hk, hv, ho, device, world, barrier, steps=3):
 
 # ---------------------------------------------------------------------------------------------- 32-layer decoder
 DECODER = dict(layers=32, hidden=4096, ffn=14336, Hq=32, Hkv=8, D=128, vocab=128256, C=128, SW=1024, prompt=16384, steps=512,
-               batch=128, micro_batch=32, p_global=0.07, p_local=0.20)
+               batch=128, micro_batch=32, p_global=0.07, p_local=0.20, retained=0.10)
 
 
 def run_decoder_leg(dc, device, rank, world, barrier):
@@ -638,23 +638,41 @@ def run_decoder_leg(dc, device, rank, world, barrier):
     g = torch.Generator(device=device).manual_seed(100 + rank)
     gc = torch.Generator(device=device).manual_seed(99)                       # the calibration pass is the same on every rank
     C, SW, N = dc['C'], dc['SW'], dc['prompt']
-    target = torch.tensor([dc['p_global'], dc['p_local']], device=device)
+    mix = torch.tensor([dc['p_global'], dc['p_local']], device=device)
 
     def fit_bias(module, args_, kwargs_):
         """Runs in front of a layer's attention during the calibration pass: fits the layer's role biases to the chunk
-        features that arrive, so that every later layer sees hidden states made under fitted roles."""
+        features that arrive, so that every later layer sees hidden states made under fitted roles.  The logits of a
+        (sequence, kv-head) vary little from chunk to chunk in the deeper layers, so the roles of a head are strongly
+        correlated and the retained fraction is not what independent chunks with the same mix would give; the share of
+        global / local chunks is therefore scaled (bisection) until the RETAINED fraction -- global chunks plus the local
+        ones behind the last global chunk -- of the calibration sequences meets the target."""
         x = (kwargs_['hidden_states'] if 'hidden_states' in kwargs_ else args_[0]).float()
-        pooled = x.unflatten(1, (-1, C)).mean(2).flatten(0, 1)                    # [chunks, hidden]
+        pooled = x.unflatten(1, (-1, C)).mean(2)                                  # [B, chunks, hidden]
         wgt = module.proj_layer.weight
         wv = wgt.view(cfg.num_key_value_heads, 3, -1)
         wv[:, :, 0] = 0
-        z = (pooled @ wgt.float().T).view(-1, cfg.num_key_value_heads, 3)       # logits without the bias column
-        f0 = pooled[:, 0].mean()
-        bias = torch.zeros(3, device=device)
-        for _ in range(80):
+        z = (pooled @ wgt.float().T).unflatten(-1, (cfg.num_key_value_heads, 3))  # [B, chunks, Hkv, 3], no bias column
+        f0 = pooled[..., 0].mean()
+        idx = torch.arange(z.shape[1], device=device)[None, :, None]
+
+        def fit(target):
+            bias = torch.zeros(3, device=device)
+            for _ in range(60):
+                r = (z + bias).argmax(-1)
+                frac = torch.stack([(r == 0).float().mean(), (r == 1).float().mean()]).clamp_min(1e-4)
+                bias[:2] += 0.5 * z.std() * (target.log() - frac.log())
             r = (z + bias).argmax(-1)
-            frac = torch.stack([(r == 0).float().mean(), (r == 1).float().mean()]).clamp_min(1e-4)
-            bias[:2] += 0.5 * z.std() * (target.log() - frac.log())
+            r[:, 0] = 0                                                           # the first chunk is always global
+            last_g = torch.where(r == 0, idx, -1).amax(1, keepdim=True)
+            kept = (r == 0).sum(1) + ((r == 1) & (idx > last_g)).sum(1)
+            return bias, (kept.float() / z.shape[1]).mean().item()
+
+        lo, hi = 0.02, 1.0
+        for _ in range(7):
+            mid = (lo * hi) ** 0.5
+            bias, kept = fit(mix * mid)
+            lo, hi = (mid, hi) if kept < dc['retained'] else (lo, mid)
         wv[:, 0, 0] = (bias[0] / f0).to(wgt.dtype)
         wv[:, 1, 0] = (bias[1] / f0).to(wgt.dtype)
 
@@ -668,6 +686,7 @@ def run_decoder_leg(dc, device, rank, world, barrier):
 
     pre_ms, dec_ms = 0.0, 0.0
     fractions = torch.zeros(dc['layers'], device=device)
+    role_mix = torch.zeros(dc['layers'], 3, device=device)
     barrier()
     for m in range(n_mb):
         ids = torch.randint(0, cfg.vocab_size, (mb, N), device=device, generator=g)
@@ -680,6 +699,7 @@ def run_decoder_leg(dc, device, rank, world, barrier):
             ev[1].record()
             for li, lc in enumerate(cache.cache_model):
                 fractions[li] += (lc.size_global_kv + lc.size_local_kv - SW).float().mean() / N / n_mb
+                role_mix[li] += model.model.layers[li].self_attn.token_states.float().mean((0, 1, 2)) / n_mb
             for _ in range(dc['steps']):
                 out = model(input_ids=tok, past_key_values=cache, use_cache=True)
                 tok = out.logits[:, -1].argmax(-1, keepdim=True)
@@ -701,6 +721,8 @@ def run_decoder_leg(dc, device, rank, world, barrier):
                 prefill_tok_per_s=dc['batch'] * N / (pre_ms * 1e-3), decode_tok_per_s=dc['batch'] * dc['steps'] / (dec_ms * 1e-3),
                 prefill_s=pre_ms * 1e-3, decode_s=dec_ms * 1e-3, logits_finite=finite,
                 retained_frac_per_layer=[round(x, 4) for x in fr], retained_frac_mean=float(np.mean(fr)),
+                retained_frac_target=dc['retained'],
+                global_local_sliding_share_mean=[round(x, 4) for x in role_mix.mean(0).cpu().tolist()],
                 note='sequences of a rank run in micro-batches (prefill and its decode steps per micro-batch); weights replicated; '
                      'no collective')
 

@@ -58,5 +58,22 @@ def build(force: bool = False, verbose: bool = False) -> str:
     return LIB
 
 
+WAIT_TEST_LIB = os.path.join(HERE, '..', 'tests', '_build', 'libnats_b200_waittest.so')
+
+
+def build_wait_test(force: bool = False) -> str:
+    """A TEST-ONLY build of the prefill entry points (never loaded by the package): every bounded wait gives up after 3 ms
+    instead of 400 ms and the K/V producer withholds one V tile per CTA, so that a test can watch a wait run out, the kernel
+    return with a status code and the context stay usable."""
+    lib = os.path.abspath(WAIT_TEST_LIB)
+    srcs = [os.path.join(CSRC, f) for f in ('prefill_sm100.cu', 'cache_ops.cu')]
+    if not force and os.path.exists(lib) and all(os.path.getmtime(x) <= os.path.getmtime(lib) for x in srcs + [__file__]):
+        return lib
+    os.makedirs(os.path.dirname(lib), exist_ok=True)
+    cmd = [_nvcc(), *NVCC_FLAGS, '-DNATS_WAIT_LIMIT_NS=3000000ull', '-DNATS_TEST_WITHHOLD_FIRST_V=1', '-shared', '-o', lib, *srcs]
+    subprocess.run(cmd, check=True)
+    return lib
+
+
 if __name__ == '__main__':
     print(build(force='--force' in sys.argv, verbose='-v' in sys.argv))

@@ -617,7 +617,13 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                     const int s = g % NS;
                     if (g >= (uint32_t)NS) ok = warp_wait<kRelaxProdNs>(smem_u32(&sm.bar_empty[s]), ((g / NS) & 1) ^ 1, abort_flag, p.status, kErrKvEmpty);
                     if (!ok) break;
-                    if (lane == 0) {
+#ifdef NATS_TEST_WITHHOLD_FIRST_V
+                    // test builds only: the V tile of a CTA's first kept tile is never loaded, so that a bounded wait runs out
+                    const bool withhold = g == 1;
+#else
+                    const bool withhold = false;
+#endif
+                    if (lane == 0 && !withhold) {
                         mbar_expect_tx(smem_u32(&sm.bar_full[s]), TILE_BYTES);
                         const CUtensorMap* map = kv == 0 ? &map_k : &map_v;
                         for (int x = 0; x < NBOX; ++x)
