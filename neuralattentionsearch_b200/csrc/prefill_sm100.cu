@@ -600,6 +600,10 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         // =============================== TMA producer ===============================
         uint32_t g = 0;                                 // ring slots filled so far (all items): two per kept tile
         const uint64_t pol_kv = l2_policy_evict_last();
+#ifdef NATS_TRACE
+        unsigned long long tr_prod_wait = 0, tr_prod_n = 0;
+        const unsigned long long tr_prod_t0 = clock64();
+#endif
         bool ok = true;
         for (int ic = 0; ok; ++ic) {
             const int slot = ic & 1;
@@ -615,7 +619,14 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
 #pragma unroll 1
                 for (int kv = 0; kv < 2 && ok; ++kv, ++g) {
                     const int s = g % NS;
+#ifdef NATS_TRACE
+                    const unsigned long long tp0 = clock64();
+#endif
                     if (g >= (uint32_t)NS) ok = warp_wait<kRelaxProdNs>(smem_u32(&sm.bar_empty[s]), ((g / NS) & 1) ^ 1, abort_flag, p.status, kErrKvEmpty);
+#ifdef NATS_TRACE
+                    tr_prod_wait += clock64() - tp0;
+                    ++tr_prod_n;
+#endif
                     if (!ok) break;
 #ifdef NATS_TEST_WITHHOLD_FIRST_V
                     // test builds only: the V tile of a CTA's first kept tile is never loaded, so that a bounded wait runs out
@@ -634,6 +645,9 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             }
             if (ok && lane == 0) mbar_arrive(smem_u32(&sm.bar_list_empty[slot]));
         }
+#ifdef NATS_TRACE
+        if (blockIdx.x == 0 && lane == 0) { g_trace[32] = tr_prod_wait; g_trace[33] = tr_prod_n; g_trace[34] = clock64() - tr_prod_t0; }
+#endif
         if (!ok) {
             // given up: let copies that are still in flight land before the shared memory is released
             for (uint32_t x = g > (uint32_t)NS ? g - NS : 0; x < g; ++x)
@@ -1021,6 +1035,12 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     }
 }
 
+}  // namespace nats
+
+#include "prefill_pair.cuh"
+
+namespace nats {
+
 // ---- host side ------------------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -1091,15 +1111,43 @@ static int launch_prefill(const CUtensorMap& mq, const CUtensorMap& mk, const CU
     return NATS_OK;
 }
 
+static int launch_prefill_pair(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const PrefillParams& p, cudaStream_t st) {
+    const size_t smem = sizeof(PairSmem);
+    int dev = 0, sms = 0;
+    NATS_CHECK_CUDA(cudaGetDevice(&dev));
+    static bool attr_set[kMaxDevices] = {};
+    if (dev < 0 || dev >= kMaxDevices || !attr_set[dev]) {
+        NATS_CHECK_CUDA(cudaFuncSetAttribute(prefill_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        if (dev >= 0 && dev < kMaxDevices) attr_set[dev] = true;
+    }
+    NATS_CHECK_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    int grid = 2 * p.total_items < sms ? 2 * p.total_items : sms;        // one persistent CTA pair per SM pair
+    grid &= ~1;
+    prefill_pair_kernel<<<grid, kPrefillThreads, smem, st>>>(mq, mk, mv, p);
+    NATS_CHECK_CUDA(cudaGetLastError());
+    return NATS_OK;
+}
+
+// CTA pairs (cta_group::2) for head_dim 128 and group sizes that are a multiple of four; NATS_B200_PAIR=0 turns them off
+static bool use_pair_kernel(int D, int nrep) {
+    static int mode = -1;
+    if (mode < 0) {
+        const char* e = getenv("NATS_B200_PAIR");
+        mode = (e != nullptr && e[0] == '1') ? 1 : 0;
+    }
+    return mode == 1 && D == 128 && nrep % 4 == 0;
+}
+
 // Tensor maps, parameters and launch shared by the entry points.  N query rows at positions q_off .. q_off + N - 1 of a
 // KV sequence of Nkv rows whose heads are kv_head_stride rows apart (0: contiguous).
 static int run_prefill(const void* d_q, const void* d_k, const void* d_v, void* d_o, int B, int Hq, int Hkv, int N, int Nkv,
                        int q_off, long long kv_head_stride, int D, int C, float sm_scale, const int32_t* lim,
                        const int32_t* tmax, const int32_t* tmin, int32_t* counter, int32_t* d_status, cudaStream_t st,
                        float* d_lse = nullptr) {
+    const bool pair = use_pair_kernel(D, Hq / Hkv);
     CUtensorMap mq, mk, mv;
     if (int rc = make_map(&mq, d_q, B * Hq, N, D, 128)) return rc;
-    if (int rc = make_map(&mk, d_k, B * Hkv, Nkv, D, 128, kv_head_stride)) return rc;
+    if (int rc = make_map(&mk, d_k, B * Hkv, Nkv, D, pair ? 64 : 128, kv_head_stride)) return rc;     // a pair's CTA loads half the rows of a K tile
     if (int rc = make_map(&mv, d_v, B * Hkv, Nkv, D, 128, kv_head_stride)) return rc;
     PrefillParams p;
     p.o = (__nv_bfloat16*)d_o; p.lse = d_lse; p.lim = lim; p.tile_max = tmax; p.tile_min = tmin; p.status = d_status;
@@ -1112,6 +1160,11 @@ static int run_prefill(const void* d_q, const void* d_k, const void* d_v, void* 
     NATS_CHECK_ARG(items <= 0x7fffffffLL - 65536, "too many work items (%lld)", items);
     p.total_items = (int)items;
     p.scale_log2 = sm_scale * 1.4426950408889634f;
+    if (pair) {
+        p.n_groups = p.nrep / 4;
+        p.total_items = B * Hkv * p.n_groups * p.Nt;
+        return launch_prefill_pair(mq, mk, mv, p, st);
+    }
     if (D == 64) return launch_prefill<64>(mq, mk, mv, p, st);
     if (D == 256) return launch_prefill<256>(mq, mk, mv, p, st);
     return launch_prefill<128>(mq, mk, mv, p, st);
