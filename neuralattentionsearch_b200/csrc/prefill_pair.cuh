@@ -168,8 +168,9 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     const int n_groups4 = p.nrep / 4;
     const int per_z = p.Nt * p.Hkv * n_groups4;
     const int total = p.total_items;                     // B * Hkv * n_groups4 * Nt
+    // round r deals items r * n_pairs ... to the pairs, in alternating direction, so that no pair always gets the heaviest
     const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
-    const int n_my_items = pair < total ? (total - pair + n_pairs - 1) / n_pairs : 0;
+    auto my_item = [&](int r) { return r * n_pairs + ((r & 1) ? n_pairs - 1 - pair : pair); };
 
     if (warp == 3) {
         // =============================== scheduler: item headers, kept-tile bitmaps, this CTA's Q tiles ===============================
@@ -181,10 +182,10 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             const int slot = ic & 1, use = ic >> 1;
             if (use > 0) ok = warp_wait<kRelaxNs>(smem_u32(&sm.bar_list_empty[slot]), (use - 1) & 1, abort_flag, p.status, kErrList);
             if (!ok) break;
-            const bool have = ic < n_my_items;
+            const int w = my_item(ic);
+            const bool have = w < total;
             int n_kept = 0;
             if (have) {
-                const int w = pair + ic * n_pairs;
                 const int z = w / per_z, rem = w - z * per_z;
                 const int y = rem / p.Nt, x = rem - y * p.Nt;
                 const int t = p.Nt - 1 - x;
@@ -305,6 +306,10 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             };
             uint32_t g = 0, gt = 0, na = 0;
             bool ok = true;
+            TR_DECL(8);
+#ifdef NATS_TRACE
+            unsigned long long tr_lock = 0, tr_pv = 0;
+#endif
             for (int ic = 0; ok; ++ic) {
                 const int slot = ic & 1;
                 ok = warp_wait(smem_u32(&sm.bar_list_full[slot]), (ic >> 1) & 1, abort_flag, p.status, kErrList);
@@ -326,20 +331,32 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 for (int j = 0; j < n && ok; ++j) {
                     const uint32_t gv = g + 2 * j + 1;
                     const int sv = gv % NS;
+                    TR(0);
                     ok = warp_wait(smem_u32(&sm.bar_full[sv]), (gv / NS) & 1, abort_flag, p.status, kErrKvFull);
+                    TR(1);
                     const bool more = j + 1 < n;
                     const uint32_t gk = gv + 1;
                     if (ok) ok = warp_wait(smem_u32(&sm.bar_p_full[h][0]), (gt + j) & 1, abort_flag, p.status, kErrPFull);
+                    TR(2);
                     if (ok && j == 0 && na > 0) ok = warp_wait(smem_u32(&sm.bar_o_empty[h]), (na - 1) & 1, abort_flag, p.status, kErrOEmpty);
+                    TR(3);
                     if (ok) ok = warp_wait(smem_u32(&sm.bar_p_full[h][1]), (gt + j) & 1, abort_flag, p.status, kErrPFull);
+                    TR(4);
                     if (ok && more) ok = warp_wait(smem_u32(&sm.bar_full[gk % NS]), (gk / NS) & 1, abort_flag, p.status, kErrKvFull);
+                    TR(5);
                     if (ok) ok = pipe_acquire(&sm.pipe_lock, lane, abort_flag, p.status);
                     if (!ok) break;
+#ifdef NATS_TRACE
+                    { const unsigned long long t_ = clock64(); tr_lock += t_ - tr_t; tr_t = t_; }
+#endif
                     tc_fence_after();
                     if (lane == 0) {
                         issue_pv(sv, j == 0);
                         if (!more) tc_commit2(smem_u32(&sm.bar_o_full[h]));
                         tc_commit2(smem_u32(&sm.bar_empty[sv]));           // frees this V slot in both CTAs
+#ifdef NATS_TRACE
+                        { const unsigned long long t_ = clock64(); tr_pv += t_ - tr_t; tr_t = t_; }
+#endif
                         if (more) {
                             issue_qk(gk % NS);
                             tc_commit2(smem_u32(&sm.bar_s_full[h]));
@@ -347,12 +364,19 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                     }
                     pipe_release(&sm.pipe_lock, lane);
                     __syncwarp();
+                    TR(6);
+#ifdef NATS_TRACE
+                    tr_acc[7] += 1;
+#endif
                 }
                 g += 2 * n;
                 gt += n;
                 ++na;
                 if (ok && lane == 0) mbar_arrive(smem_u32(&sm.bar_list_empty[slot]));
             }
+#ifdef NATS_TRACE
+            if (h == 0) { TR_DUMP(16, 8); if (tr_on) { g_trace[24] = tr_lock; g_trace[25] = tr_pv; } }
+#endif
         }
     } else {
         // =============================== softmax + epilogue (both CTAs) ===============================
@@ -370,12 +394,14 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         uint32_t gt = 0, na = 0, g = 0;
         const bool releaser = (warp & 3) == 0 && lane == 0;
         bool ok = true;
+        TR_DECL(10);
         for (int ic = 0; ok; ++ic) {
             const int slot = ic & 1;
             ok = warp_wait(smem_u32(&sm.bar_list_full[slot]), (ic >> 1) & 1, abort_flag, p.status, kErrList);
             if (!ok) break;
             const ItemHeader hd = sm.item[slot];
             if (!hd.valid) break;
+            TR(8);
             const int n = hd.n_kept;
             const int qpos = p.q_off + hd.t * kTile + row;
             const int32_t* lim = p.lim + (size_t)hd.bh * p.Nc;
@@ -400,9 +426,11 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                         }
                     }
                 }
+                TR(0);
                 ok = warp_wait(smem_u32(&sm.bar_s_full[h]), gt & 1, abort_flag, p.status, kErrSFull);
                 if (!ok) break;
                 tc_fence_after();
+                TR(1);
                 if (releaser) {
                     // Q.K^T of tile j has completed in both CTAs: this head slot is done with this CTA's half of K_j and, on the
                     // item's last tile, with its Q tile
@@ -413,6 +441,7 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 #pragma unroll
                 for (int c = 0; c < 4; ++c) tmem_ld32(tS + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&sreg[c * 32]));
                 tc_wait_ld();
+                TR(2);
                 if (partial) {
 #pragma unroll
                     for (int i = 0; i < kTile; ++i)
@@ -449,6 +478,7 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                     }
                 }
                 const float m_neg = (m_ref == -INFINITY) ? 0.f : -m_ref;
+                TR(3);
                 const uint64_t scale2 = pack2(scale, scale), mneg2 = pack2(m_neg, m_neg);
                 uint64_t ls2 = pack2(0.f, 0.f);
 #pragma unroll
@@ -472,6 +502,9 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                     tc_fence_before();
                     __syncwarp();
                     if (lane == 0) mbar_arrive_cluster(pf_leader[half]);
+#ifdef NATS_TRACE
+                    if (half == 0) TR(4); else TR(5);
+#endif
                 }
                 {
                     float a, b;
@@ -480,7 +513,9 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 }
             }
             // epilogue
+            TR(0);
             if (ok) ok = warp_wait(smem_u32(&sm.bar_o_full[h]), na & 1, abort_flag, p.status, kErrOFull);
+            TR(6);
             if (ok) {
                 tc_fence_after();
                 const float inv = l_sum > 0.f ? 1.f / l_sum : 0.f;
@@ -513,9 +548,16 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             }
             ++na;
             g += 2 * n;
+            TR(7);
+#ifdef NATS_TRACE
+            tr_acc[9] += n;
+#endif
             __syncwarp();
             if (ok && lane == 0) mbar_arrive(smem_u32(&sm.bar_list_empty[slot]));
         }
+#ifdef NATS_TRACE
+        if (warp == 4) TR_DUMP(0, 10);
+#endif
     }
     // ---- teardown: nobody leaves while the other CTA may still touch its shared memory or TMEM ----
     tc_fence_before();

@@ -959,3 +959,41 @@ def test_a_wait_that_runs_out_returns_a_status_and_leaves_the_context_usable():
     good = prefill_attention(qd, kd, vd, roles, C, SW)      # product library, same context
     check_status(dev())
     assert_close_attn(good, orc.prefill_attention(q, k, v, roles_np, C, SW), 'after the timed-out launch')
+
+
+PAIR_CHILD = r'''
+import sys, numpy as np, torch
+sys.path.insert(0, sys.argv[1])
+from neuralattentionsearch_b200 import check_status, prefill_attention
+d = np.load(sys.argv[2])
+dev = torch.device('cuda:0')
+q, k, v = (torch.from_numpy(d[n]).to(dev).bfloat16() for n in ('q', 'k', 'v'))
+o = prefill_attention(q, k, v, torch.from_numpy(d['roles']).to(dev), int(d['C']), int(d['SW']))
+check_status(dev)
+np.save(sys.argv[3], o.float().cpu().numpy())
+'''
+
+
+@pytest.mark.parametrize('B,Hq,Hkv,N,C,SW', [(2, 8, 2, 1500, 32, 256), (1, 4, 1, 4096, 128, 512)])
+def test_cta_pair_kernel_equals_the_single_cta_kernel(B, Hq, Hkv, N, C, SW, tmp_path):
+    """The opt-in kernel that runs a query tile of four heads on a cluster of two CTAs (NATS_B200_PAIR=1, read when the
+    library is first used, hence a child process): same tiles, same order of accumulation, so the same bits as the default
+    kernel, and within tolerance of the oracle."""
+    import os
+    import subprocess
+    import sys
+    from neuralattentionsearch_b200 import check_status, prefill_attention
+    D = 128
+    roles = orc.make_roles(B, Hkv, -(-N // C), 0.08, 0.25, seed=N)
+    q, k, v = inputs(B, Hq, Hkv, N, D, seed=N + 1)
+    single = prefill_attention(q.to(dev()).bfloat16(), k.to(dev()).bfloat16(), v.to(dev()).bfloat16(), torch.from_numpy(roles).to(dev()), C, SW)
+    check_status(dev())
+    np.savez(tmp_path / 'in.npz', q=q.numpy(), k=k.numpy(), v=v.numpy(), roles=roles, C=C, SW=SW)
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, NATS_B200_PAIR='1')
+    r = subprocess.run([sys.executable, '-c', PAIR_CHILD, root, str(tmp_path / 'in.npz'), str(tmp_path / 'out.npy')], env=env,
+                       capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stderr[-2000:]
+    pair = torch.from_numpy(np.load(tmp_path / 'out.npy'))
+    assert_close_attn(pair, orc.prefill_attention(q, k, v, roles, C, SW), 'pair kernel')
+    assert torch.equal(pair, single.float().cpu())
