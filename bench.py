@@ -599,7 +599,7 @@ def run_copy_floor_leg(hq, hk, hv, ho, device, world, barrier, steps=3):
 
 # ---------------------------------------------------------------------------------------------- 32-layer decoder
 DECODER = dict(layers=32, hidden=4096, ffn=14336, Hq=32, Hkv=8, D=128, vocab=128256, C=128, SW=1024, prompt=16384, steps=512,
-               batch=128, micro_batch=32, p_global=0.07, p_local=0.20, retained=0.10)
+               batch=128, micro_batch=32, p_global=0.07, p_local=0.20, retained=0.10, eager_steps=8)
 
 
 def run_decoder_leg(dc, device, rank, world, barrier):
@@ -608,7 +608,7 @@ def run_decoder_leg(dc, device, rank, world, barrier):
     the batch is split over the ranks (weights replicated) and runs in micro-batches on each."""
     from transformers import LlamaConfig, LlamaForCausalLM
     from neuralattentionsearch_b200 import NAtSCache, check_status
-    from neuralattentionsearch_b200.hf import TransformerArgs, enable_llama_nats_chunk_eval
+    from neuralattentionsearch_b200.hf import GraphedGreedyDecoder, TransformerArgs, enable_llama_nats_chunk_eval
     cfg = LlamaConfig(hidden_size=dc['hidden'], intermediate_size=dc['ffn'], num_hidden_layers=dc['layers'],
                       num_attention_heads=dc['Hq'], num_key_value_heads=dc['Hkv'], head_dim=dc['D'], vocab_size=dc['vocab'],
                       max_position_embeddings=32768, rope_theta=500000.0)
@@ -684,14 +684,14 @@ def run_decoder_leg(dc, device, rank, world, barrier):
             h.remove()
     torch.cuda.synchronize(device)
 
-    pre_ms, dec_ms = 0.0, 0.0
+    pre_ms, dec_ms, replay_ms, eager_ms = 0.0, 0.0, 0.0, 0.0
     fractions = torch.zeros(dc['layers'], device=device)
     role_mix = torch.zeros(dc['layers'], 3, device=device)
     barrier()
     for m in range(n_mb):
         ids = torch.randint(0, cfg.vocab_size, (mb, N), device=device, generator=g)
         cache = NAtSCache(SW, C)
-        ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(5)]
         with torch.no_grad():
             ev[0].record()
             out = model(input_ids=ids, past_key_values=cache, use_cache=True, logits_to_keep=1)
@@ -700,18 +700,32 @@ def run_decoder_leg(dc, device, rank, world, barrier):
             for li, lc in enumerate(cache.cache_model):
                 fractions[li] += (lc.size_global_kv + lc.size_local_kv - SW).float().mean() / N / n_mb
                 role_mix[li] += model.model.layers[li].self_attn.token_states.float().mean((0, 1, 2)) / n_mb
-            for _ in range(dc['steps']):
+            # greedy decoding, every step replayed from one CUDA graph (recorded once per micro-batch: the recording and the
+            # step that runs in front of it are inside the timed region) ...
+            head = min(16, dc['steps'] - 1)
+            dec = GraphedGreedyDecoder(model, cache, dc['steps'])
+            toks = dec.generate(tok, head)
+            ev[3].record()
+            toks = dec.generate(toks[:, -1:], dc['steps'] - head)
+            ev[2].record()
+            # ... and a few steps of the eager loop over the same modules on the same cache, for comparison
+            tok = toks[:, -1:]
+            for _ in range(dc['eager_steps']):
                 out = model(input_ids=tok, past_key_values=cache, use_cache=True)
                 tok = out.logits[:, -1].argmax(-1, keepdim=True)
-            ev[2].record()
+            ev[4].record()
         torch.cuda.synchronize(device)
         pre_ms += ev[0].elapsed_time(ev[1])
         dec_ms += ev[1].elapsed_time(ev[2])
-        finite = bool(torch.isfinite(out.logits.float()).all())
-        del cache, out
+        replay_ms += ev[3].elapsed_time(ev[2])
+        eager_ms += ev[2].elapsed_time(ev[4])
+        finite = bool(torch.isfinite(out.logits.float()).all() and torch.isfinite(dec.logits.float()).all())
+        del cache, out, dec
     check_status(device)
     barrier()
     pre_ms, dec_ms = allmax(pre_ms, device, world), allmax(dec_ms, device, world)
+    replay_ms, eager_ms = allmax(replay_ms, device, world), allmax(eager_ms, device, world)
+    head = min(16, dc['steps'] - 1)
     fr = fractions.cpu().tolist()
     del model
     torch.cuda.empty_cache()
@@ -719,6 +733,11 @@ def run_decoder_leg(dc, device, rank, world, barrier):
                       'NAtS attention in every layer (chunk 128, window 1024)',
                 batch=dc['batch'], sequences_per_gpu=per_rank, micro_batch=mb, prompt_tokens=N, decode_steps=dc['steps'],
                 prefill_tok_per_s=dc['batch'] * N / (pre_ms * 1e-3), decode_tok_per_s=dc['batch'] * dc['steps'] / (dec_ms * 1e-3),
+                decode_replay_tok_per_s=dc['batch'] * (dc['steps'] - head) / (replay_ms * 1e-3),
+                decode_eager_tok_per_s=dc['batch'] * dc['eager_steps'] / (eager_ms * 1e-3), eager_steps=dc['eager_steps'],
+                decode_note='decode_tok_per_s: all steps of hf.GraphedGreedyDecoder including the recording of its CUDA graph (once per '
+                            'micro-batch); decode_replay_tok_per_s: the steps after the first 16; decode_eager_tok_per_s: the eager loop over the '
+                            'patched Hugging Face model on the same cache (host bound)',
                 prefill_s=pre_ms * 1e-3, decode_s=dec_ms * 1e-3, logits_finite=finite,
                 retained_frac_per_layer=[round(x, 4) for x in fr], retained_frac_mean=float(np.mean(fr)),
                 retained_frac_target=dc['retained'],

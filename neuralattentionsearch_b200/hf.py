@@ -154,3 +154,115 @@ def enable_llama_nats_chunk_eval(model, transformer_args, n_options: int = 3, ex
 def enable_mistral_nats_chunk_eval(model, transformer_args, n_options: int = 3, executor=None):
     """hf/mistral_nats_chunk.py: the Mistral attention module has the same projections and cache hand-over."""
     return _enable_eval(model, transformer_args, n_options, executor)
+
+
+class GraphedGreedyDecoder:
+    """Greedy decoding of a model patched by ``enable_llama_nats_chunk_eval`` / ``enable_mistral_nats_chunk_eval`` with
+    every step replayed from ONE CUDA graph.
+
+    A decode step of the patched Hugging Face model is a few hundred small launches (per layer: norms, five projections,
+    RoPE + head split, append + attention + placement, MLP) behind as much Python; at batch sizes where the GPU work of a
+    step is a few milliseconds the host is the bottleneck.  This class runs the same modules with the same arithmetic
+    (the role head pools the layer's normalised hidden states over the chunk exactly as the cache's
+    ``update_nats_cached_x_in_chunk`` does, the cache step is ``decode_step_static``) but keeps every step-to-step
+    quantity on the device -- token, position, tokens in the unfinished chunk, the pooled hidden states -- so that the
+    step has static launch parameters, records it once and replays it.  The reference has no counterpart (its decode loop
+    is eager PyTorch: hf_pred.py / eval_efficiency.py).
+
+    Use: prefill through the model as usual (``model(input_ids, past_key_values=cache, ...)``), then
+    ``GraphedGreedyDecoder(model, cache, max_steps).generate(first_token, n)``; afterwards the cache is where ``n``
+    eager decode steps would have left it and can be used by either path."""
+
+    def __init__(self, model, cache: NAtSCache, max_steps: int):
+        core = model.model
+        attn0 = core.layers[0].self_attn
+        cfg = attn0.config
+        if attn0.chunk_merge_method != 'mean':
+            raise NotImplementedError('graphed decoding pools the hidden states with "mean" only')
+        if len(cache.cache_model) != len(core.layers):
+            raise ValueError('prefill the prompt through the model first: the cache has no state for some layers')
+        self.model, self.cache = model, cache
+        self.C = attn0.chunk_size
+        self.n_heads, self.n_kv, self.hd = cfg.num_attention_heads, cfg.num_key_value_heads, attn0.head_dim
+        lc0 = cache.cache_model[0]
+        start = cache.get_seq_length(0)
+        if start < self.C:
+            raise ValueError('graphed decoding starts behind the first chunk (the first chunk of a sequence is forced global on the host)')
+        dev = next(model.parameters()).device
+        dt = core.embed_tokens.weight.dtype
+        B = lc0.bsz
+        self.device, self.B = dev, B
+        self.tok = torch.zeros(B, 1, dtype=torch.long, device=dev)
+        self.pos = torch.full((1, 1), start, dtype=torch.long, device=dev)
+        self.fill = torch.full((1,), lc0.chunk_fill_size, dtype=torch.int32, device=dev)
+        self.acc = []
+        for li in range(len(core.layers)):
+            cur = cache.get_nats_cached_x_in_chunk(li) if lc0.chunk_fill_size else None
+            self.acc.append(torch.zeros(B, 1, cfg.hidden_size, dtype=dt, device=dev) if cur is None else cur.to(dt).clone())
+        self.o_buf = torch.empty(B, self.n_heads, 1, self.hd, dtype=torch.bfloat16, device=dev)
+        self.logits = None
+        for lc in cache.cache_model:
+            lc.prepare_static_decode(max_steps, self.n_heads, self.hd)
+        self.steps_left = max_steps
+        self.graph = None
+
+    def _step(self, recording: bool) -> None:
+        core, C, B = self.model.model, self.C, self.B
+        x = core.embed_tokens(self.tok)
+        cos, sin = core.rotary_emb(x, self.pos)
+        last = self.fill == C - 1                               # this token completes its chunk (device flag)
+        scale = self.hd ** -0.5
+        for li, layer in enumerate(core.layers):
+            attn = layer.self_attn
+            h = layer.input_layernorm(x)
+            pooled = self.acc[li] + h / C                       # as NAtSCache.merge_new_x_values_in_chunk
+            logit = attn.proj_layer(pooled).unflatten(-1, (self.n_kv, attn.n_options))
+            roles = logit.max(-1)[1][:, 0].to(torch.uint8).contiguous()   # [B, n_kv]; read on the device only if `last`
+            self.acc[li].copy_(torch.where(last, torch.zeros_like(pooled), pooled))
+            q, k, v = F_.rope_split_heads(attn.q_proj(h), attn.k_proj(h), attn.v_proj(h), cos, sin, self.n_heads, self.n_kv, self.hd)
+            self.cache.cache_model[li].decode_step_static(q, k, v, roles, self.o_buf, scale, recording=True)
+            x = x + attn.o_proj(self.o_buf.transpose(1, 2).reshape(B, 1, -1).to(x.dtype))
+            x = x + layer.mlp(layer.post_attention_layernorm(x))
+        logits = self.model.lm_head(core.norm(x))
+        if self.logits is None:
+            self.logits = torch.empty_like(logits)
+        self.logits.copy_(logits)
+        self.tok.copy_(logits[:, -1].argmax(-1, keepdim=True))
+        self.pos.add_(1)
+        self.fill.copy_(torch.where(last, torch.zeros_like(self.fill), self.fill + 1))
+
+    @torch.no_grad()
+    def generate(self, first_token: torch.Tensor, n_steps: int) -> torch.Tensor:
+        """Feeds ``first_token`` [B,1] and decodes ``n_steps`` tokens greedily; returns them as [B, n_steps].  ``self.logits``
+        holds the logits of the last step."""
+        if n_steps < 1 or n_steps > self.steps_left:
+            raise ValueError(f'{n_steps} steps asked for, room for {self.steps_left}')
+        out = torch.empty(self.B, n_steps, dtype=torch.long, device=self.device)
+        self.tok.copy_(first_token.reshape(self.B, 1))
+        done = 0
+        if self.graph is None:
+            # one step outside the graph on a side stream, as graph capture asks (library workspaces, lazy initialisation)
+            side = torch.cuda.Stream(self.device)
+            side.wait_stream(torch.cuda.current_stream(self.device))
+            with torch.cuda.stream(side):
+                self._step(recording=False)
+            torch.cuda.current_stream(self.device).wait_stream(side)
+            out[:, 0].copy_(self.tok[:, 0])
+            done = 1
+            self.graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(self.graph):
+                self._step(recording=True)                      # captured, not run
+        for i in range(done, n_steps):
+            self.graph.replay()
+            out[:, i].copy_(self.tok[:, 0])
+        self._note_steps(n_steps)
+        return out
+
+    def _note_steps(self, n: int) -> None:
+        """Brings the host's view of the cache to where ``n`` eager decode steps would have left it."""
+        self.steps_left -= n
+        for lc in self.cache.cache_model:
+            lc.note_static_steps(n)
+        fill = self.cache.cache_model[0].chunk_fill_size
+        for li in range(len(self.acc)):
+            self.cache._set_cached_x(self.acc[li].clone() if fill else None, li)

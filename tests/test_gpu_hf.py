@@ -212,3 +212,50 @@ def test_patched_mistral_segments_match_one_call():
         assert torch.equal(a.size_global_kv, b.size_global_kv) and torch.equal(a.size_local_kv, b.size_local_kv)
         roles = model.model.layers[a.layer_id].self_attn.token_states
         assert roles is not None
+
+
+@pytest.mark.parametrize('N', [64, 61])                      # prompt ends on a chunk boundary / inside a chunk
+def test_graphed_greedy_decoder_equals_the_eager_decode_loop(N):
+    """Greedy decoding with every step replayed from one CUDA graph: same tokens, same logits and the same cache as the
+    eager loop over the patched model, across several chunk completions; afterwards the eager path continues from the
+    graphed decoder's cache."""
+    from neuralattentionsearch_b200 import NAtSCache, check_status
+    from neuralattentionsearch_b200.hf import GraphedGreedyDecoder, TransformerArgs, enable_llama_nats_chunk_eval
+    C, SW, steps, more = 8, 32, 29, 5
+    model = tiny_llama(seed=5)
+    enable_llama_nats_chunk_eval(model, TransformerArgs(n_msks=2, chunk_size=C, local_seq_max_length=SW))
+    torch.manual_seed(6)
+    for layer in model.model.layers:
+        layer.self_attn.proj_layer.weight.data.normal_(0, 0.5)
+    ids = torch.randint(0, 512, (3, N), device=dev())
+    with torch.no_grad():
+        # eager loop
+        c1 = NAtSCache(SW, C)
+        out = model(input_ids=ids, past_key_values=c1, use_cache=True)
+        first = out.logits[:, -1].argmax(-1, keepdim=True)
+        tok, eager = first, []
+        for _ in range(steps + more):
+            out = model(input_ids=tok, past_key_values=c1, use_cache=True)
+            tok = out.logits[:, -1].argmax(-1, keepdim=True)
+            eager.append(tok)
+        eager = torch.cat(eager, 1)
+        # graphed loop, then the eager path on the same cache
+        c2 = NAtSCache(SW, C)
+        out2 = model(input_ids=ids, past_key_values=c2, use_cache=True)
+        assert torch.equal(out2.logits[:, -1].argmax(-1, keepdim=True), first)
+        dec = GraphedGreedyDecoder(model, c2, max_steps=steps)
+        got = dec.generate(first, 10)
+        got = torch.cat([got, dec.generate(got[:, -1:], steps - 10)], 1)
+        tok = got[:, -1:]
+        tail = []
+        for _ in range(more):
+            out2 = model(input_ids=tok, past_key_values=c2, use_cache=True)
+            tok = out2.logits[:, -1].argmax(-1, keepdim=True)
+            tail.append(tok)
+    check_status(dev())
+    assert torch.equal(got, eager[:, :steps])
+    assert torch.equal(torch.cat(tail, 1), eager[:, steps:])
+    assert torch.equal(out2.logits, out.logits)
+    for a, b in zip(c1.cache_model, c2.cache_model):
+        assert torch.equal(a.size_global_kv, b.size_global_kv) and torch.equal(a.size_local_kv, b.size_local_kv)
+        assert (a.n_ctx_data, a.chunk_fill_size, a.sliding_queue_tail, a.get_seq_length()) == (b.n_ctx_data, b.chunk_fill_size, b.sliding_queue_tail, b.get_seq_length())
