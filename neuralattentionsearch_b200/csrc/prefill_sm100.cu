@@ -9,7 +9,7 @@
 //   warp 3      scheduler: fetches the next item, builds its kept-tile bitmap while the current item runs, loads its Q tiles
 //   warps 1,2   MMA issuers of head slot 0 / 1 (one elected lane each): S_h = Q_h.K^T (SS, N = 128), O_h += P_h.V (TS, P from TMEM)
 //   warps 4-7   softmax of head slot 0: one thread per query row, the 128-entry score row read with tcgen05.ld, online
-//   warps 8-11  softmax of head slot 1  softmax in registers, P written back over S as packed bf16 in two halves
+//   warps 8-11  softmax of head slot 1  softmax in registers, P written back over S as packed bf16
 //
 // Which KV tiles are visited comes from the role bitmap: a bitmap of kept tiles is built in shared memory from the
 // per-tile max / min row limits (nats_b200_role_prep); tiles without a visible entry are never loaded.  Only tiles
@@ -405,6 +405,12 @@ __device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatil
 // MMAs in the order they were queued, so batches that interleaved would finish together and keep the two heads in step --
 // both in their softmax, then both waiting for the tensor pipe.  With whole batches one head's scores are ready a batch
 // earlier than the other's, and from then on one head's softmax overlaps the other head's MMAs.
+#ifndef NATS_P_ONCE
+#define NATS_P_ONCE 1
+#endif
+#if NATS_P_ONCE && NATS_PV_EARLY
+#error "the early first half of P.V needs the halves of P published one by one"
+#endif
 #ifndef NATS_PIPE_LOCK
 #define NATS_PIPE_LOCK 1
 #endif
@@ -452,8 +458,9 @@ __device__ __forceinline__ void pipe_release(int* lock, int lane) {
 // current one has completed, and a head's epilogue only delays that head's own chain.
 //
 // Per head and kept tile j the chain is  S = Q.K_j^T (8 or 4 MMAs of N = 128)  ->  softmax over the 128-entry row held in
-// registers  ->  P (bf16) over the first 64 columns of S, published in two halves of 64 keys  ->  O += P.V_j (the MMAs of
-// the first 64 keys are issued while the second half of P is still being computed)  ->  S = Q.K_{j+1}^T.  The two heads
+// registers  ->  P (bf16) over the first 64 columns of S, handed over once per tile (a hand-over per half of 64 keys costs
+// the softmax warps a second wait + fence + arrive and buys nothing, because a batch is queued whole: 1.16 against 1.13 ms)
+// ->  O += P.V_j  ->  S = Q.K_{j+1}^T.  The two heads
 // run this chain half a period apart, so that one head's softmax (MUFU and issue slots of the four SM sub-partitions)
 // overlaps the other head's MMAs on the tensor pipe.
 template <int D>
@@ -655,7 +662,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         }
     } else if (warp == 1 || warp == 2) {
         // =============================== MMA issuers: warp 1 for head slot 0, warp 2 for head slot 1 ===============================
-        // Per head and kept tile j:  O_h += P_j.V_j in two halves (as the halves of P arrive), then S_h = Q_h.K_{j+1}^T,
+        // Per head and kept tile j:  O_h += P_j.V_j, then S_h = Q_h.K_{j+1}^T,
         // which overwrites P_j: the tensor pipe runs one thread's MMAs in issue order.  A ring slot is released when both
         // issuers have committed the MMAs that read it; an issuer whose head slot is empty in an item (odd group size)
         // only keeps the barrier counts going.
@@ -733,7 +740,9 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                 const bool more = j + 1 < n;
                 const uint32_t gk = gv + 1;
                 if (ok && active) {
+#if !NATS_P_ONCE
                     ok = warp_wait(smem_u32(&sm.bar_p_full[h][0]), (gt + j) & 1, abort_flag, p.status, kErrPFull);
+#endif
                     TR(2);
                     // the first P.V of an item overwrites O_h: the previous item's epilogue must have read it
                     if (ok && j == 0 && na > 0) ok = warp_wait(smem_u32(&sm.bar_o_empty[h]), (na - 1) & 1, abort_flag, p.status, kErrOEmpty);
@@ -945,10 +954,20 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                             }
                             tmem_st16(tS + half * 32 + c * 16, pk);
                         }
+#if NATS_P_ONCE
+                        // a batch is queued when all of P is there: one hand-over per tile (wait, fence, arrive), not one per half
+                        if (half == 1) {
+                            tc_wait_st();
+                            tc_fence_before();
+                            __syncwarp();                         // every lane's row of P is in TMEM and fenced
+                            if (lane == 0) mbar_arrive(smem_u32(&sm.bar_p_full[h][1]));
+                        }
+#else
                         tc_wait_st();
                         tc_fence_before();
                         __syncwarp();                             // every lane's half of P is in TMEM and fenced
                         if (lane == 0) mbar_arrive(smem_u32(&sm.bar_p_full[h][half]));
+#endif
 #ifdef NATS_TRACE
                         if (half == 0) TR(4); else TR(5);
 #endif
