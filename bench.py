@@ -805,7 +805,9 @@ def main():
         if rank != 0:
             return
         threads = os.cpu_count() or 1
-        r = run_cpu_leg(w, max(args.steps, 1), max(0, args.warmup), threads)       # exactly the steps and warm-up asked for (time-boxed)
+        # the steps and warm-up asked for, time-boxed; never fewer than 5 timed runs, so that the median means something
+        # (`steps_run` says how many ran)
+        r = run_cpu_leg(w, max(args.steps, 5), max(1, args.warmup), threads)
         line = dict(metric=METRIC, value=r['value'], unit='TFLOP/s', n_gpus=args.gpus, steps=args.steps, warmup=args.warmup,
                     ms_per_step=r['seconds_per_step'] * 1e3, higher_is_better=True, scaling='weak', vs_baseline=None,
                     dtype='f32', data='synthetic', config=config, impl='reference', steps_run=r['steps'],
