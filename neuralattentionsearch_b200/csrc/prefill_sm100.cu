@@ -34,12 +34,6 @@ constexpr int kPrefillThreads = 384;
 // setmaxnreg split: 128 * low + 256 * high must not exceed the 384 * 168 registers of the launch
 constexpr int kRegsLow = NATS_REGS_LOW, kRegsHigh = NATS_REGS_HIGH;
 static_assert(128 * kRegsLow + 256 * kRegsHigh <= 384 * 168, "setmaxnreg budget");
-#ifndef NATS_F32X2
-#define NATS_F32X2 1
-#endif
-#ifndef NATS_MAX3
-#define NATS_MAX3 1
-#endif
 constexpr uint32_t kBoxBytes = 128 * 64 * 2;            // one TMA box: 128 rows x 64 bf16, 128-byte swizzled
 #ifndef NATS_RELAX_NS
 #define NATS_RELAX_NS 200
@@ -288,38 +282,10 @@ __device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
     asm("add.rn.ftz.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
     return d;
 }
-// 2^x for two values on the FMA and ALU pipes instead of the MUFU: round x to the nearest integer n with the
-// 1.5 * 2^23 trick, a cubic for 2^(x - n) on [-0.5, 0.5] (relative error 1.4e-4, far below the bf16 rounding of P), and n
-// added to the exponent field.  x is clamped at -126 (masked entries are -inf), which leaves about 1e-38 instead of 0.
-#ifndef NATS_POLY
-#define NATS_POLY 0
-#endif
-__device__ __forceinline__ void exp2_poly2(uint64_t x2, float& p0, float& p1) {
-    float x0, x1;
-    unpack2(x2, x0, x1);
-    const uint64_t xc = pack2(fmaxf(x0, -126.f), fmaxf(x1, -126.f));
-    const uint64_t magic = pack2(12582912.f, 12582912.f), neg_magic = pack2(-12582912.f, -12582912.f);
-    const uint64_t t2 = add2(xc, magic);
-    const uint64_t n2 = add2(t2, neg_magic);
-    const uint64_t f2 = fma2(n2, pack2(-1.f, -1.f), xc);
-    uint64_t q2 = fma2(f2, pack2(0.055029310f, 0.055029310f), pack2(0.24225681f, 0.24225681f));
-    q2 = fma2(q2, f2, pack2(0.69325304f, 0.69325304f));
-    q2 = fma2(q2, f2, pack2(0.99995136f, 0.99995136f));
-    float t0, t1, q0, q1;
-    unpack2(t2, t0, t1);
-    unpack2(q2, q0, q1);
-    p0 = __int_as_float(__float_as_int(q0) + (__float_as_int(t0) << 23));
-    p1 = __int_as_float(__float_as_int(q1) + (__float_as_int(t1) << 23));
-}
-
 __device__ __forceinline__ float max3(float a, float b, float c) {
-#if NATS_MAX3
     float d;
     asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
     return d;
-#else
-    return fmaxf(fmaxf(a, b), c);
-#endif
 }
 
 #ifdef NATS_TRACE
@@ -405,23 +371,10 @@ __device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatil
 // MMAs in the order they were queued, so batches that interleaved would finish together and keep the two heads in step --
 // both in their softmax, then both waiting for the tensor pipe.  With whole batches one head's scores are ready a batch
 // earlier than the other's, and from then on one head's softmax overlaps the other head's MMAs.
-#ifndef NATS_P_ONCE
-#define NATS_P_ONCE 1
-#endif
-#if NATS_P_ONCE && NATS_PV_EARLY
-#error "the early first half of P.V needs the halves of P published one by one"
-#endif
 #ifndef NATS_LOCK_SLEEP_NS
 #define NATS_LOCK_SLEEP_NS 0       // pause between attempts to take the lock (0: none; 40 ns and 100 ns were measured slower)
 #endif
-#ifndef NATS_PIPE_LOCK
-#define NATS_PIPE_LOCK 1
-#endif
-#ifndef NATS_PV_EARLY
-#define NATS_PV_EARLY 0
-#endif
 __device__ __forceinline__ bool pipe_acquire(int* lock, int lane, volatile int* abort_flag, int32_t* status) {
-#if NATS_PIPE_LOCK
     int got = 1;
     if (lane == 0) {
         if (atomicCAS(lock, 0, 1) != 0) {
@@ -443,15 +396,10 @@ __device__ __forceinline__ bool pipe_acquire(int* lock, int lane, volatile int* 
         }
     }
     return __shfl_sync(0xffffffffu, got, 0) != 0;
-#else
-    return true;
-#endif
 }
 __device__ __forceinline__ void pipe_release(int* lock, int lane) {
-#if NATS_PIPE_LOCK
     __syncwarp();
     if (lane == 0) atomicExch(lock, 0);
-#endif
 }
 
 // Persistent kernel: every CTA takes work items (query tile x kv-head x head pair) from a global counter until none is
@@ -743,19 +691,9 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                 const bool more = j + 1 < n;
                 const uint32_t gk = gv + 1;
                 if (ok && active) {
-#if !NATS_P_ONCE
-                    ok = warp_wait(smem_u32(&sm.bar_p_full[h][0]), (gt + j) & 1, abort_flag, p.status, kErrPFull);
-#endif
                     TR(2);
                     // the first P.V of an item overwrites O_h: the previous item's epilogue must have read it
                     if (ok && j == 0 && na > 0) ok = warp_wait(smem_u32(&sm.bar_o_empty[h]), (na - 1) & 1, abort_flag, p.status, kErrOEmpty);
-#if NATS_PV_EARLY
-                    // the first half of P.V goes to the tensor pipe while the second half of P is still being computed
-                    if (!ok) break;
-                    tc_fence_after();
-                    if (lane == 0) issue_pv_half(sv, 0, j == 0);
-                    __syncwarp();
-#endif
                     TR(3);
                     if (ok) ok = warp_wait(smem_u32(&sm.bar_p_full[h][1]), (gt + j) & 1, abort_flag, p.status, kErrPFull);
                     TR(4);
@@ -773,9 +711,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                 tc_fence_after();
                 if (lane == 0) {
                     if (active) {
-#if !NATS_PV_EARLY
                         issue_pv_half(sv, 0, j == 0);
-#endif
                         issue_pv_half(sv, 1, false);
                         if (!more) tc_commit(smem_u32(&sm.bar_o_full[h]));
                         tc_commit(smem_u32(&sm.bar_empty[sv]));        // V_j is free as soon as P.V has run: the ring is short
@@ -919,14 +855,9 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                     }
                     const float m_neg = (m_ref == -INFINITY) ? 0.f : -m_ref;
                     TR(3);
-                    // P = exp2(S * scale - m), row sum in fp32, P packed to bf16 over the first 64 columns of S; each half
-                    // (64 keys) is published as soon as it is stored
-#if NATS_F32X2
+                    // P = exp2(S * scale - m), row sum in fp32, P packed to bf16 over the first 64 columns of S
                     const uint64_t scale2 = pack2(scale, scale), mneg2 = pack2(m_neg, m_neg);
                     uint64_t ls2 = pack2(0.f, 0.f);
-#else
-                    float ls0 = 0.f, ls1 = 0.f;
-#endif
 #pragma unroll
                     for (int half = 0; half < 2; ++half) {
 #pragma unroll
@@ -935,29 +866,15 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                             const int base = half * 64 + c * 32;
 #pragma unroll
                             for (int i = 0; i < 32; i += 2) {
-#if NATS_F32X2
                                 const uint64_t x2 = fma2(pack2(__uint_as_float(sreg[base + i]), __uint_as_float(sreg[base + i + 1])), scale2, mneg2);
-                                float p0, p1;
-                                if (NATS_POLY > 0 && ((i / 2) % (NATS_POLY > 0 ? NATS_POLY : 1)) == NATS_POLY - 1) {
-                                    exp2_poly2(x2, p0, p1);        // a share of the exponentials runs beside the MUFU
-                                } else {
-                                    float x0, x1;
-                                    unpack2(x2, x0, x1);
-                                    p0 = ex2(x0);
-                                    p1 = ex2(x1);
-                                }
+                                float x0, x1;
+                                unpack2(x2, x0, x1);
+                                const float p0 = ex2(x0), p1 = ex2(x1);
                                 ls2 = add2(ls2, pack2(p0, p1));
-#else
-                                const float p0 = ex2(fmaf(__uint_as_float(sreg[base + i]), scale, m_neg));
-                                const float p1 = ex2(fmaf(__uint_as_float(sreg[base + i + 1]), scale, m_neg));
-                                ls0 += p0;
-                                ls1 += p1;
-#endif
                                 pk[i / 2] = pack_bf16(p0, p1);
                             }
                             tmem_st16(tS + half * 32 + c * 16, pk);
                         }
-#if NATS_P_ONCE
                         // a batch is queued when all of P is there: one hand-over per tile (wait, fence, arrive), not one per half
                         if (half == 1) {
                             tc_wait_st();
@@ -965,25 +882,15 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                             __syncwarp();                         // every lane's row of P is in TMEM and fenced
                             if (lane == 0) mbar_arrive(smem_u32(&sm.bar_p_full[h][1]));
                         }
-#else
-                        tc_wait_st();
-                        tc_fence_before();
-                        __syncwarp();                             // every lane's half of P is in TMEM and fenced
-                        if (lane == 0) mbar_arrive(smem_u32(&sm.bar_p_full[h][half]));
-#endif
 #ifdef NATS_TRACE
                         if (half == 0) TR(4); else TR(5);
 #endif
                     }
-#if NATS_F32X2
                     {
                         float a, b;
                         unpack2(ls2, a, b);
                         l_sum += a + b;
                     }
-#else
-                    l_sum += ls0 + ls1;
-#endif
                 }
                 // epilogue: O / l -> bf16 -> global; O_h is handed back to the issuer as soon as it sits in registers
                 TR(0);
