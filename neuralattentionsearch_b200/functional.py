@@ -117,6 +117,17 @@ class _PinnedWords:
             cls._free.setdefault(dev, []).append(word)
 
 
+_side_streams: dict = {}
+
+
+def _side_stream(device: torch.device) -> torch.cuda.Stream:
+    """One extra stream per device for small read-backs that must not sit between two kernels of the caller's stream."""
+    st = _side_streams.get(device.index)
+    if st is None:
+        st = _side_streams[device.index] = torch.cuda.Stream(device)
+    return st
+
+
 class _AsyncWord:
     """An int32 scalar on its way from the device to the host, with the device's prefill status word riding along.
     Calling the object waits for the copy and returns the value (and raises if a kernel that ran before the copy had
@@ -125,10 +136,19 @@ class _AsyncWord:
     def __init__(self, src: torch.Tensor):
         self.dev = src.device
         self.word = _PinnedWords.take(self.dev)
-        self.word[:1].copy_(src[:1], non_blocking=True)
-        self.word[1:].copy_(status_word(self.dev), non_blocking=True)
-        self.done = torch.cuda.Event()
-        self.done.record(torch.cuda.current_stream(self.dev))
+        # The two small copies run on a side stream behind what the current stream holds so far: on the current stream they
+        # would stand between the kernel that wrote ``src`` and the (long) kernel the caller launches next, ~10 us per step.
+        main = torch.cuda.current_stream(self.dev)
+        side = _side_stream(self.dev)
+        ready = torch.cuda.Event()
+        ready.record(main)
+        side.wait_event(ready)
+        with torch.cuda.stream(side):
+            self.word[:1].copy_(src[:1], non_blocking=True)
+            self.word[1:].copy_(status_word(self.dev), non_blocking=True)
+            self.done = torch.cuda.Event()
+            self.done.record(side)
+        src.record_stream(side)
 
     def __call__(self) -> int:
         self.done.synchronize()
