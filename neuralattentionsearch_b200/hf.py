@@ -205,6 +205,7 @@ class GraphedGreedyDecoder:
             lc.prepare_static_decode(max_steps, self.n_heads, self.hd)
         self.steps_left = max_steps
         self.graph = None
+        self._seen = start                  # tokens the cache must hold when generate() is called
 
     def _step(self, recording: bool) -> None:
         core, C, B = self.model.model, self.C, self.B
@@ -237,6 +238,10 @@ class GraphedGreedyDecoder:
         holds the logits of the last step."""
         if n_steps < 1 or n_steps > self.steps_left:
             raise ValueError(f'{n_steps} steps asked for, room for {self.steps_left}')
+        if self.cache.get_seq_length(0) != self._seen:
+            # token position, chunk fill and pooled hidden states live on the device: they are only right if nobody else
+            # has moved the cache since this object last did
+            raise RuntimeError('the cache has been used by another path since this decoder was built: build a new GraphedGreedyDecoder')
         out = torch.empty(self.B, n_steps, dtype=torch.long, device=self.device)
         self.tok.copy_(first_token.reshape(self.B, 1))
         done = 0
@@ -256,6 +261,7 @@ class GraphedGreedyDecoder:
             self.graph.replay()
             out[:, i].copy_(self.tok[:, 0])
         self._note_steps(n_steps)
+        self._seen = self.cache.get_seq_length(0)
         return out
 
     def _note_steps(self, n: int) -> None:

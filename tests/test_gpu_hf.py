@@ -259,3 +259,10 @@ def test_graphed_greedy_decoder_equals_the_eager_decode_loop(N):
     for a, b in zip(c1.cache_model, c2.cache_model):
         assert torch.equal(a.size_global_kv, b.size_global_kv) and torch.equal(a.size_local_kv, b.size_local_kv)
         assert (a.n_ctx_data, a.chunk_fill_size, a.sliding_queue_tail, a.get_seq_length()) == (b.n_ctx_data, b.chunk_fill_size, b.sliding_queue_tail, b.get_seq_length())
+    with pytest.raises(ValueError):
+        dec.generate(tok, 1)                                   # no room left
+    dec2 = GraphedGreedyDecoder(model, c2, max_steps=4)
+    with torch.no_grad():
+        model(input_ids=tok, past_key_values=c2, use_cache=True)
+    with pytest.raises(RuntimeError):
+        dec2.generate(tok, 1)                                  # the eager path moved the cache behind the decoder's back
